@@ -218,7 +218,8 @@ def known_architectures():
 
 
 def config_from_json_dict(d: Dict[str, Any]):
-    arch = (d.get("architectures") or [None])[0]
+    # the architecture's name: the first of ``architectures``, or the string ``architecture``
+    arch = (d.get("architectures") or [d.get("architecture")])[0]
     if arch not in _CONFIG_CLASSES:
         raise ConfigError(f"config.json: architecture {arch!r} is not registered "
                           f"(known: {', '.join(known_architectures()) or 'none'})")

@@ -163,6 +163,116 @@ BSPEC_API int bspec_add_rmsnorm(float* resid, const void* delta, int delta_dtype
   return BSPEC_LAUNCH_CHECK();
 }
 
+// ---------------------------------------------------------------- add + layer norm
+// resid[t,:] += delta[t,:] (if delta);  out[t,:] = (resid - mean) * rsqrt(var + eps) * w + b, var the mean of the
+// squared deviations (taken in a second pass over the row, from the mean, not as E[x^2] - mean^2).  All float32;
+// one rounding, to the output type, at the end.  One block per row; rows of up to 4 * VPT * blockDim.x elements
+// (a multiple of 4) stay in registers between the passes, others are read again.
+template <typename TD, typename TO, int VPT>
+__global__ void add_layernorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                         const void* __restrict__ weight, const void* __restrict__ bias, int w_dtype,
+                                         TO* __restrict__ out, int d, float eps) {
+  bspec::pdl_prologue(14);
+  __shared__ float scratch[32];
+  const size_t base = (size_t)blockIdx.x * d;
+  float x[VPT][4];
+  float s = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = 4 * (threadIdx.x + k * blockDim.x);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x[k][j] = 0.f;
+    if (i < d) {
+      load4<float>(resid + base + i, x[k]);
+      if (delta != nullptr) {
+        float dl[4];
+        load4<TD>(delta + base + i, dl);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[k][j] += dl[j];
+        store4<float>(resid + base + i, x[k]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s += x[k][j];
+    }
+  }
+  const float mean = block_sum(s, scratch) / (float)d;
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = 4 * (threadIdx.x + k * blockDim.x);
+    if (i < d) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        x[k][j] -= mean;
+        ss += x[k][j] * x[k][j];
+      }
+    }
+  }
+  const float r = rsqrtf(block_sum(ss, scratch) / (float)d + eps);
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = 4 * (threadIdx.x + k * blockDim.x);
+    if (i < d) {
+      float y[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        y[j] = to_f32(from_f32<TO>(x[k][j] * r * load_as_f32(weight, w_dtype, i + j) + load_as_f32(bias, w_dtype, i + j)));
+      store4<TO>(out + base + i, y);
+    }
+  }
+}
+
+template <typename TD, typename TO>
+__global__ void add_layernorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                     const void* __restrict__ weight, const void* __restrict__ bias, int w_dtype,
+                                     TO* __restrict__ out, int d, float eps) {
+  bspec::pdl_prologue(14);
+  __shared__ float scratch[32];
+  const size_t base = (size_t)blockIdx.x * d;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = resid[base + i];
+    if (delta != nullptr) {
+      v += to_f32(delta[base + i]);
+      resid[base + i] = v;
+    }
+    s += v;
+  }
+  const float mean = block_sum(s, scratch) / (float)d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = resid[base + i] - mean;
+    ss += v * v;
+  }
+  const float r = rsqrtf(block_sum(ss, scratch) / (float)d + eps);
+  for (int i = threadIdx.x; i < d; i += blockDim.x)
+    out[base + i] = from_f32<TO>((resid[base + i] - mean) * r * load_as_f32(weight, w_dtype, i) + load_as_f32(bias, w_dtype, i));
+}
+
+BSPEC_API int bspec_add_layernorm(float* resid, const void* delta, int delta_dtype, const void* weight, const void* bias,
+                                  int w_dtype, void* out, int out_dtype, int n, int d, float eps, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (delta_dtype == out_dtype && d % 4 == 0 && d <= 4 * 4 * 1024) {
+    const int quads = d / 4;
+    int threads = quads >= 1024 ? 1024 : ((quads + 31) / 32) * 32;
+    if (threads < 32) threads = 32;
+    const int vpt = (quads + threads - 1) / threads;
+#define LV(TD, TO, V) BSPEC_LAUNCH((add_layernorm_vec_kernel<TD, TO, V>), n, threads, 0, stream, resid, (const TD*)delta, weight, bias, w_dtype, (TO*)out, d, eps)
+    if (out_dtype == BSPEC_F32) { if (vpt <= 1) LV(float, float, 1); else if (vpt <= 2) LV(float, float, 2); else LV(float, float, 4); }
+    else { if (vpt <= 1) LV(__nv_bfloat16, __nv_bfloat16, 1); else if (vpt <= 2) LV(__nv_bfloat16, __nv_bfloat16, 2); else LV(__nv_bfloat16, __nv_bfloat16, 4); }
+#undef LV
+    return BSPEC_LAUNCH_CHECK();
+  }
+  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+#define L(TD, TO) BSPEC_LAUNCH((add_layernorm_kernel<TD, TO>), n, threads, 0, stream, resid, (const TD*)delta, weight, bias, w_dtype, (TO*)out, d, eps)
+  if (delta_dtype == BSPEC_F32 && out_dtype == BSPEC_F32) L(float, float);
+  else if (delta_dtype == BSPEC_BF16 && out_dtype == BSPEC_BF16) L(__nv_bfloat16, __nv_bfloat16);
+  else if (delta_dtype == BSPEC_F32 && out_dtype == BSPEC_BF16) L(float, __nv_bfloat16);
+  else L(__nv_bfloat16, float);
+#undef L
+  return BSPEC_LAUNCH_CHECK();
+}
+
 // ---------------------------------------------------------------- row gather (+ pending add)
 template <typename TD>
 __global__ void gather_rows_add_kernel(const float* __restrict__ resid, const TD* __restrict__ pending,
@@ -259,6 +369,75 @@ BSPEC_API int bspec_silu_mul(const void* u, void* m, int dtype, int n, int inter
   else
     BSPEC_LAUNCH((silu_mul_kernel<__nv_bfloat16>), blocks, threads, 0, stream, (const __nv_bfloat16*)u,
                  (__nv_bfloat16*)m, inter, total, group);
+  return BSPEC_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- clamped GLU:  g sigmoid(alpha g) (u + 1)
+// u [n, 2I] -> m [n, I] with g = min(gate, limit), u = clamp(up, -limit, limit); the column layouts of silu_mul.
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ u, T* __restrict__ m, int inter, size_t total, int group,
+                                   float alpha, float limit) {
+  bspec::pdl_prologue(15);
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = idx / inter, col = idx - row * inter;
+    const float g = fminf(to_f32(u[row * 2 * inter + gate_col(col, inter, group)]), limit);
+    const float up = fminf(fmaxf(to_f32(u[row * 2 * inter + up_col(col, inter, group)]), -limit), limit);
+    m[idx] = from_f32<T>(g / (1.f + expf(-alpha * g)) * (up + 1.f));
+  }
+}
+
+BSPEC_API int bspec_clamped_glu(const void* u, void* m, int dtype, int n, int inter, int group, float alpha,
+                                float limit, cudaStream_t stream) {
+  const size_t total = (size_t)n * inter;
+  if (total == 0) return 0;
+  if (group < 0 || (group > 0 && inter % group != 0)) return (int)cudaErrorInvalidValue;
+  const int threads = 256;
+  size_t want = (total + threads - 1) / threads;
+  const size_t cap = (size_t)bspec::sm_count() * 32;
+  const int blocks = (int)(want > cap ? cap : want);
+  if (dtype == BSPEC_F32)
+    BSPEC_LAUNCH((clamped_glu_kernel<float>), blocks, threads, 0, stream, (const float*)u, (float*)m, inter, total, group, alpha, limit);
+  else
+    BSPEC_LAUNCH((clamped_glu_kernel<__nv_bfloat16>), blocks, threads, 0, stream, (const __nv_bfloat16*)u,
+                 (__nv_bfloat16*)m, inter, total, group, alpha, limit);
+  return BSPEC_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- exact GELU in place:  0.5 x (1 + erf(x / sqrt 2))
+template <typename T>
+__global__ void gelu_erf_kernel(T* __restrict__ x, size_t total) {
+  bspec::pdl_prologue(16);
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const float v = to_f32(x[idx]);
+    x[idx] = from_f32<T>(0.5f * v * (1.f + erff(v * 0.70710678118654752440f)));
+  }
+}
+
+BSPEC_API int bspec_gelu_erf(void* x, int dtype, long long total, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  const int threads = 256;
+  size_t want = ((size_t)total + threads - 1) / threads;
+  const size_t cap = (size_t)bspec::sm_count() * 32;
+  const int blocks = (int)(want > cap ? cap : want);
+  if (dtype == BSPEC_F32) BSPEC_LAUNCH((gelu_erf_kernel<float>), blocks, threads, 0, stream, (float*)x, (size_t)total);
+  else BSPEC_LAUNCH((gelu_erf_kernel<__nv_bfloat16>), blocks, threads, 0, stream, (__nv_bfloat16*)x, (size_t)total);
+  return BSPEC_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- soft cap in place:  cap * tanh(x / cap)
+__global__ void tanh_softcap_kernel(float* __restrict__ x, size_t total, float cap) {
+  bspec::pdl_prologue(17);
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
+    x[idx] = cap * tanhf(x[idx] / cap);
+}
+
+BSPEC_API int bspec_tanh_softcap(float* x, long long total, float cap, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  const int threads = 256;
+  size_t want = ((size_t)total + threads - 1) / threads;
+  const size_t cap_blocks = (size_t)bspec::sm_count() * 32;
+  BSPEC_LAUNCH((tanh_softcap_kernel), (int)(want > cap_blocks ? cap_blocks : want), threads, 0, stream, x, (size_t)total, cap);
   return BSPEC_LAUNCH_CHECK();
 }
 
@@ -462,10 +641,12 @@ BSPEC_API int bspec_rope_kv_append(void* qkv, int dtype, int n, int Hq, int Hkv,
 }
 
 // Rotary encoding alone, on a strided view x [n, H, hd] (row stride given in elements).
+// ``hd`` is the distance between heads in elements (a view that holds only the rotated part of wider heads has a
+// head stride larger than rot); ``magnitude`` multiplies cosine and sine (1 for a plain rotation).
 template <typename T>
 __global__ void rope_inplace_kernel(T* __restrict__ x, long long row_stride, int H, int hd,
                                     const float* __restrict__ inv_freq, int rot, int interleaved,
-                                    const int* __restrict__ positions) {
+                                    const int* __restrict__ positions, float magnitude) {
   bspec::pdl_prologue(6);
   extern __shared__ float cs[];
   const int t = blockIdx.x, half = rot / 2;
@@ -473,8 +654,8 @@ __global__ void rope_inplace_kernel(T* __restrict__ x, long long row_stride, int
   for (int j = threadIdx.x; j < half; j += blockDim.x) {
     float s, c;
     rope_sincos(pos, inv_freq, half, j, &s, &c);
-    cs[j] = c;
-    cs[half + j] = s;
+    cs[j] = c * magnitude;
+    cs[half + j] = s * magnitude;
   }
   __syncthreads();
   T* row = x + (size_t)t * row_stride;
@@ -490,13 +671,13 @@ __global__ void rope_inplace_kernel(T* __restrict__ x, long long row_stride, int
 }
 
 BSPEC_API int bspec_rope_inplace(void* x, int dtype, int n, long long row_stride, int H, int hd, const float* inv_freq,
-                                 int rot, int interleaved, const int* positions, cudaStream_t stream) {
+                                 int rot, int interleaved, const int* positions, float magnitude, cudaStream_t stream) {
   if (n <= 0 || rot <= 0) return 0;
   const size_t smem = (size_t)rot * sizeof(float);
   if (dtype == BSPEC_F32)
-    BSPEC_LAUNCH((rope_inplace_kernel<float>), n, 128, smem, stream, (float*)x, row_stride, H, hd, inv_freq, rot, interleaved, positions);
+    BSPEC_LAUNCH((rope_inplace_kernel<float>), n, 128, smem, stream, (float*)x, row_stride, H, hd, inv_freq, rot, interleaved, positions, magnitude);
   else
-    BSPEC_LAUNCH((rope_inplace_kernel<__nv_bfloat16>), n, 128, smem, stream, (__nv_bfloat16*)x, row_stride, H, hd, inv_freq, rot, interleaved, positions);
+    BSPEC_LAUNCH((rope_inplace_kernel<__nv_bfloat16>), n, 128, smem, stream, (__nv_bfloat16*)x, row_stride, H, hd, inv_freq, rot, interleaved, positions, magnitude);
   return BSPEC_LAUNCH_CHECK();
 }
 

@@ -9,8 +9,12 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
 __global__ void __launch_bounds__(256)
 sgemm_tn_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C, int M, int N, int K,
-                long long lda, long long ldw, long long ldc) {
+                long long lda, long long ldw, long long ldc, long long sa, long long sw, long long sc) {
   bspec::pdl_prologue(10);
+  // a batch of products along grid z: operand b starts b * (sa, sw, sc) elements further on
+  A += (size_t)blockIdx.z * sa;
+  W += (size_t)blockIdx.z * sw;
+  C += (size_t)blockIdx.z * sc;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -65,7 +69,18 @@ BSPEC_API int bspec_sgemm_tn(const float* A, const float* W, float* C, int M, in
   if (M <= 0 || N <= 0) return 0;
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) return (int)cudaErrorInvalidConfiguration;
-  BSPEC_LAUNCH((sgemm_tn_kernel), grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
+  BSPEC_LAUNCH((sgemm_tn_kernel), grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc, 0ll, 0ll, 0ll);
+  return BSPEC_LAUNCH_CHECK();
+}
+
+// `batch` products C_b = A_b * W_b^T whose operands lie sa / sw / sc elements apart.
+BSPEC_API int bspec_sgemm_tn_batched(const float* A, const float* W, float* C, int M, int N, int K, long long lda,
+                                     long long ldw, long long ldc, long long sa, long long sw, long long sc, int batch,
+                                     cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || batch <= 0) return 0;
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
+  if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidConfiguration;
+  BSPEC_LAUNCH((sgemm_tn_kernel), grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc, sa, sw, sc);
   return BSPEC_LAUNCH_CHECK();
 }
 

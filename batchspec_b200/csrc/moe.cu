@@ -1,0 +1,296 @@
+// Routed feed-forward (mixture of experts): the router, the plan that sorts (token, choice) slots by expert, a
+// grouped matrix product over the sorted rows, and the weighted sum that brings the rows back to their tokens.
+//
+//   route     per token: z = Wr h in float32, s = sigmoid(z), choice = s + correction; the experts come in equal
+//             groups of neighbours, a group's score is the sum of its two largest choices, only the best `keep`
+//             groups stay (the others count as minus infinity); the `top` largest choices are taken, ties to the
+//             lower index; weights = s of the chosen * scale (no renormalisation)
+//   plan      one block: counts per expert, a stable counting sort of the n*top slots by expert (row r of the
+//             sorted order holds slot perm[r]; inv[slot] = r), and the list of row tiles (expert, first row, rows)
+//   grouped   C[r, :] = act(A[src(r), :] . W[expert(r)]^T) over the tiles of the plan; every output element is one
+//             thread's sum over k in ascending order, so a row's result does not depend on where it was sorted to
+//   combine   out[t, :] = sum_k weight[t, k] * Y[inv[t*top + k], :], k ascending, float32
+//
+// Nothing here reads a count on the host: grids are sized by upper bounds and surplus blocks leave at once, so the
+// kernels can be captured in a graph.
+#include "common.cuh"
+#include <math.h>
+using namespace bspec;
+
+namespace {
+
+constexpr int ROUTE_THREADS = 128;
+constexpr int MAX_EXPERTS = 1024;
+
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_THREADS)
+moe_route_kernel(const T* __restrict__ h, int d, const T* __restrict__ wr, const void* __restrict__ corr,
+                 int corr_dtype, int E, int G, int keep, int top, float scale, int* __restrict__ ids,
+                 float* __restrict__ wts) {
+  bspec::pdl_prologue(50);
+  extern __shared__ float sm[];
+  float* hs = sm;                 // [d]
+  float* sc = hs + d;             // [E] sigmoid scores
+  float* ch = sc + E;             // [E] choice scores (masked in place)
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) hs[i] = to_f32(h[(size_t)t * d + i]);
+  __syncthreads();
+  for (int e = warp; e < E; e += ROUTE_THREADS / 32) {
+    const T* w = wr + (size_t)e * d;
+    float z = 0.f;
+    for (int i = lane; i < d; i += 32) z += hs[i] * to_f32(w[i]);
+    z = warp_sum(z);
+    if (lane == 0) {
+      const float s = 1.f / (1.f + expf(-z));
+      sc[e] = s;
+      ch[e] = s + (corr != nullptr ? load_as_f32(corr, corr_dtype, e) : 0.f);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  if (G > 1 && keep < G) {
+    const int per = E / G;
+    // group scores into the start of hs (no longer needed)
+    for (int g = 0; g < G; ++g) {
+      float a = -INFINITY, b = -INFINITY;       // the two largest
+      for (int j = 0; j < per; ++j) {
+        const float v = ch[g * per + j];
+        if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+      }
+      hs[g] = per > 1 ? a + b : a;
+    }
+    // keep the best `keep` groups: mark them by taking their score out
+    for (int k = 0; k < keep; ++k) {
+      int best = -1;
+      float bv = -INFINITY;
+      for (int g = 0; g < G; ++g) {
+        const float v = hs[g];
+        if (!isnan(v) && (best < 0 || v > bv)) { best = g; bv = v; }
+      }
+      if (best >= 0) hs[best] = NAN;            // NaN marks a kept group
+    }
+    for (int g = 0; g < G; ++g)
+      if (!isnan(hs[g]))
+        for (int j = 0; j < per; ++j) ch[g * per + j] = -INFINITY;
+  }
+  for (int k = 0; k < top; ++k) {
+    int best = 0;
+    float bv = -INFINITY;
+    bool found = false;
+    for (int e = 0; e < E; ++e) {
+      const float v = ch[e];
+      if (!isnan(v) && (!found || v > bv)) { best = e; bv = v; found = true; }
+    }
+    ids[(size_t)t * top + k] = best;
+    wts[(size_t)t * top + k] = sc[best] * scale;
+    ch[best] = NAN;                             // taken
+  }
+}
+
+// One block of 1024 threads.  tiles: int [max_tiles][3] = {expert, first sorted row, rows}; n_tiles_out: int [1].
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ ids, int slots, int E, int BM, int* __restrict__ perm, int* __restrict__ inv,
+                int* __restrict__ offsets, int* __restrict__ tiles, int* __restrict__ n_tiles_out, int max_tiles) {
+  bspec::pdl_prologue(51);
+  __shared__ int cnt[MAX_EXPERTS + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int e = warp; e < E; e += nwarps) {
+    int c = 0;
+    for (int s0 = 0; s0 < slots; s0 += 32) {
+      const int s = s0 + lane;
+      c += __popc(__ballot_sync(0xffffffffu, s < slots && ids[s] == e));
+    }
+    if (lane == 0) cnt[e] = c;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0, nt = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = cnt[e];
+      cnt[e] = run;
+      offsets[e] = run;
+      for (int r = 0; r < c && nt < max_tiles; r += BM) {
+        tiles[3 * nt] = e;
+        tiles[3 * nt + 1] = run + r;
+        tiles[3 * nt + 2] = min(BM, c - r);
+        ++nt;
+      }
+      run += c;
+    }
+    cnt[E] = run;
+    offsets[E] = run;
+    *n_tiles_out = nt;
+  }
+  __syncthreads();
+  for (int e = warp; e < E; e += nwarps) {
+    int at = cnt[e];
+    for (int s0 = 0; s0 < slots; s0 += 32) {
+      const int s = s0 + lane;
+      const bool mine = s < slots && ids[s] == e;
+      const unsigned mask = __ballot_sync(0xffffffffu, mine);
+      if (mine) {
+        const int r = at + __popc(mask & ((1u << lane) - 1u));
+        perm[r] = s;
+        inv[s] = r;
+      }
+      at += __popc(mask);
+    }
+  }
+}
+
+__device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f)); }
+
+// A [*, K] rows; row r of the sorted order reads A[perm[r] / top] when perm is given (the up projection), else
+// A[r] (the down projection).  W [E, N, K].  C [slots, N].  Thread tiles of TM x 4, 16 x 16 threads.
+template <typename T, typename TO, int BM, bool GELU>
+__global__ void __launch_bounds__(256)
+moe_grouped_kernel(const T* __restrict__ A, const int* __restrict__ perm, int top, const T* __restrict__ W,
+                   TO* __restrict__ C, int N, int K, const int* __restrict__ tiles, const int* __restrict__ n_tiles) {
+  bspec::pdl_prologue(52);
+  constexpr int BN = 64, BK = 16, TM = BM / 16, TN = 4;
+  if ((int)blockIdx.y >= *n_tiles) return;
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Ws[BK][BN + 4];
+  __shared__ int src[BM];
+  const int e = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+  const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
+  const int n0 = blockIdx.x * BN;
+  if (tid < BM) src[tid] = tid < rows ? (perm != nullptr ? perm[row0 + tid] / top : row0 + tid) : -1;
+  __syncthreads();
+  const T* We = W + (size_t)e * N * K;
+  float acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    for (int idx = tid; idx < BM * BK; idx += 256) {
+      const int r = idx / BK, k = k0 + idx % BK;
+      As[idx % BK][r] = (src[r] >= 0 && k < K) ? to_f32(A[(size_t)src[r] * K + k]) : 0.f;
+    }
+    for (int idx = tid; idx < BN * BK; idx += 256) {
+      const int r = idx / BK, k = k0 + idx % BK;
+      Ws[idx % BK][r] = (n0 + r < N && k < K) ? to_f32(We[(size_t)(n0 + r) * K + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      float a[TM], b[TN];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) a[i] = As[k][ty * TM + i];
+#pragma unroll
+      for (int j = 0; j < TN; ++j) b[j] = Ws[k][tx * TN + j];
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int r = ty * TM + i;
+    if (r >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int n = n0 + tx * TN + j;
+      if (n < N) C[(size_t)(row0 + r) * N + n] = from_f32<TO>(GELU ? gelu_erf(acc[i][j]) : acc[i][j]);
+    }
+  }
+}
+
+// sorted[r, :] = h[perm[r] / top, :]
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ h, const int* __restrict__ perm, int top, T* __restrict__ out,
+                                  int d) {
+  bspec::pdl_prologue(53);
+  const size_t src = (size_t)(perm[blockIdx.x] / top) * d, dst = (size_t)blockIdx.x * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) out[dst + i] = h[src + i];
+}
+
+template <typename TY, typename TO>
+__global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ inv, const float* __restrict__ wts,
+                                   int top, TO* __restrict__ out, int d) {
+  bspec::pdl_prologue(54);
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) acc += wts[(size_t)t * top + k] * to_f32(y[(size_t)inv[(size_t)t * top + k] * d + i]);
+    out[(size_t)t * d + i] = from_f32<TO>(acc);
+  }
+}
+
+}  // namespace
+
+BSPEC_API int bspec_moe_route(const void* h, int dtype, int n, int d, const void* wr, const void* corr, int corr_dtype,
+                              int E, int G, int keep, int top, float scale, int* ids, float* wts,
+                              cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (E <= 0 || E > MAX_EXPERTS || top <= 0 || top > E || G <= 0 || E % G || keep <= 0 || keep > G ||
+      (long long)keep * (E / G) < top)
+    return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)(d + 2 * E + 8) * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  if (dtype == BSPEC_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    BSPEC_LAUNCH((moe_route_kernel<float>), n, ROUTE_THREADS, smem, stream, (const float*)h, d, (const float*)wr, corr,
+                 corr_dtype, E, G, keep, top, scale, ids, wts);
+  } else {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    BSPEC_LAUNCH((moe_route_kernel<__nv_bfloat16>), n, ROUTE_THREADS, smem, stream, (const __nv_bfloat16*)h, d,
+                 (const __nv_bfloat16*)wr, corr, corr_dtype, E, G, keep, top, scale, ids, wts);
+  }
+  return BSPEC_LAUNCH_CHECK();
+}
+
+BSPEC_API int bspec_moe_plan(const int* ids, int slots, int E, int BM, int* perm, int* inv, int* offsets, int* tiles,
+                             int* n_tiles, int max_tiles, cudaStream_t stream) {
+  if (slots <= 0) return 0;
+  if (E <= 0 || E > MAX_EXPERTS || (BM != 16 && BM != 64)) return (int)cudaErrorInvalidValue;
+  BSPEC_LAUNCH((moe_plan_kernel), 1, 1024, 0, stream, ids, slots, E, BM, perm, inv, offsets, tiles, n_tiles, max_tiles);
+  return BSPEC_LAUNCH_CHECK();
+}
+
+BSPEC_API int bspec_moe_grouped(const void* A, const int* perm, int top, const void* W, void* C, int dtype,
+                                int out_dtype, int N, int K, const int* tiles, const int* n_tiles, int max_tiles,
+                                int BM, int gelu, cudaStream_t stream) {
+  if (max_tiles <= 0 || N <= 0) return 0;
+  dim3 grid((N + 63) / 64, max_tiles);
+  if (grid.y > 65535) return (int)cudaErrorInvalidConfiguration;
+#define LK(T, TO, B, G) BSPEC_LAUNCH((moe_grouped_kernel<T, TO, B, G>), grid, 256, 0, stream, (const T*)A, perm, top, \
+                                     (const T*)W, (TO*)C, N, K, tiles, n_tiles)
+#define LB(T, TO) do { if (BM == 64) { if (gelu) LK(T, TO, 64, true); else LK(T, TO, 64, false); }                  \
+                       else { if (gelu) LK(T, TO, 16, true); else LK(T, TO, 16, false); } } while (0)
+  if (dtype == BSPEC_F32) LB(float, float);
+  else if (out_dtype == BSPEC_F32) LB(__nv_bfloat16, float);
+  else LB(__nv_bfloat16, __nv_bfloat16);
+#undef LB
+#undef LK
+  return BSPEC_LAUNCH_CHECK();
+}
+
+BSPEC_API int bspec_moe_gather(const void* h, int dtype, const int* perm, int top, void* out, int slots, int d,
+                               cudaStream_t stream) {
+  if (slots <= 0) return 0;
+  if (dtype == BSPEC_F32)
+    BSPEC_LAUNCH((moe_gather_kernel<float>), slots, 128, 0, stream, (const float*)h, perm, top, (float*)out, d);
+  else
+    BSPEC_LAUNCH((moe_gather_kernel<__nv_bfloat16>), slots, 128, 0, stream, (const __nv_bfloat16*)h, perm, top,
+                 (__nv_bfloat16*)out, d);
+  return BSPEC_LAUNCH_CHECK();
+}
+
+BSPEC_API int bspec_moe_combine(const void* y, int y_dtype, const int* inv, const float* wts, int top, void* out,
+                                int out_dtype, int n, int d, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int threads = d >= 1024 ? 256 : 128;
+#define LC(TY, TO) BSPEC_LAUNCH((moe_combine_kernel<TY, TO>), n, threads, 0, stream, (const TY*)y, inv, wts, top, (TO*)out, d)
+  if (y_dtype == BSPEC_F32 && out_dtype == BSPEC_F32) LC(float, float);
+  else if (y_dtype == BSPEC_F32) LC(float, __nv_bfloat16);
+  else if (out_dtype == BSPEC_F32) LC(__nv_bfloat16, float);
+  else LC(__nv_bfloat16, __nv_bfloat16);
+#undef LC
+  return BSPEC_LAUNCH_CHECK();
+}
+
+BSPEC_DEFINE_TRACE_SETTER(bspec_trace_set_moe)

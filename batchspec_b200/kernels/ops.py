@@ -45,7 +45,29 @@ _SIGNATURES = {
     "bspec_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "bspec_rope_kv_append": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p],
-    "bspec_rope_inplace": [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
+    "bspec_rope_inplace": [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_float,
+                           c_void_p],
+    "bspec_add_layernorm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float,
+                            c_void_p],
+    "bspec_clamped_glu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+    "bspec_gelu_erf": [c_void_p, c_int, c_longlong, c_void_p],
+    "bspec_tanh_softcap": [c_void_p, c_longlong, c_float, c_void_p],
+    "bspec_latent_prepare": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float,
+                             c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                             c_int, c_longlong, c_void_p],
+    "bspec_latent_attention_generic": [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p,
+                                       c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_void_p],
+    "bspec_gate_heads": [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "bspec_moe_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                        c_void_p, c_void_p, c_void_p],
+    "bspec_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "bspec_moe_grouped": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                          c_int, c_int, c_int, c_void_p],
+    "bspec_moe_gather": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+    "bspec_moe_combine": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "bspec_sgemm_tn_batched": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
+                               c_longlong, c_longlong, c_longlong, c_int, c_void_p],
     "bspec_attention_generic": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_longlong, c_void_p],
     "bspec_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
@@ -103,10 +125,14 @@ def set_pdl(on: bool) -> None:
 
 
 _TRACE_SETTERS = ["bspec_trace_set_attention_tcgen05", "bspec_trace_set_elementwise", "bspec_trace_set_attention_generic", "bspec_trace_set_attention_bf16",
-                  "bspec_trace_set_gemm_fp32", "bspec_trace_set_sampling", "bspec_trace_set_gemm_tcgen05"]
+                  "bspec_trace_set_gemm_fp32", "bspec_trace_set_sampling", "bspec_trace_set_gemm_tcgen05", "bspec_trace_set_latent",
+                  "bspec_trace_set_moe"]
 TRACE_KERNEL_NAMES = {1: "embed", 2: "add_rmsnorm", 3: "gather_rows_add", 4: "silu_mul", 5: "rope_kv_append",
                       6: "rope_inplace", 7: "attn_generic", 8: "attn_decode", 9: "attn_prefill", 10: "sgemm",
-                      11: "sample_threshold", 12: "sample_pick", 13: "sample_final", 20: "gemm_tcgen05", 30: "attn_prefill_tc"}
+                      11: "sample_threshold", 12: "sample_pick", 13: "sample_final", 14: "add_layernorm", 15: "clamped_glu",
+                      16: "gelu_erf", 17: "tanh_softcap", 20: "gemm_tcgen05", 30: "attn_prefill_tc", 40: "latent_prepare",
+                      41: "latent_attn_generic", 42: "gate_heads", 43: "latent_attn_mma", 44: "latent_attn_join",
+                      50: "moe_route", 51: "moe_plan", 52: "moe_grouped", 53: "moe_gather", 54: "moe_combine"}
 
 
 def set_trace(buf: Optional[torch.Tensor], count: Optional[torch.Tensor]) -> None:
@@ -204,6 +230,47 @@ def gather_rows_add(resid: torch.Tensor, pending: Optional[torch.Tensor], rows: 
            "gather_rows_add")
 
 
+def add_layernorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, bias: torch.Tensor,
+                  eps: float, out: torch.Tensor) -> None:
+    """resid += delta (if given), out = (resid - mean) / sqrt(var + eps) * weight + bias, in float32."""
+    _require_cuda(resid, delta, weight, bias, out)
+    assert resid.dtype == torch.float32 and resid.is_contiguous() and out.is_contiguous()
+    n, d = resid.shape
+    assert out.shape == resid.shape and weight.numel() == d and bias.numel() == d and weight.dtype == bias.dtype
+    if delta is not None:
+        assert delta.shape == resid.shape and delta.is_contiguous()
+    dd = _dtype_code(delta.dtype) if delta is not None else _dtype_code(out.dtype)
+    _check(load_library().bspec_add_layernorm(resid.data_ptr(), _ptr(delta), dd, weight.data_ptr(), bias.data_ptr(),
+                                              _dtype_code(weight.dtype), out.data_ptr(), _dtype_code(out.dtype),
+                                              n, d, float(eps), _stream()), "add_layernorm")
+
+
+def clamped_glu(u: torch.Tensor, out: torch.Tensor, alpha: float, limit: float, group: int = 0) -> None:
+    """out = g * sigmoid(alpha * g) * (up + 1) with g = min(gate, limit), up = clamp(up, -limit, limit); the column
+    layouts of ``silu_mul``."""
+    _require_cuda(u, out)
+    n, inter = out.shape
+    assert u.shape == (n, 2 * inter) and u.dtype == out.dtype and u.is_contiguous() and out.is_contiguous()
+    _check(load_library().bspec_clamped_glu(u.data_ptr(), out.data_ptr(), _dtype_code(u.dtype), n, inter, int(group),
+                                            float(alpha), float(limit), _stream()), "clamped_glu")
+
+
+def tanh_softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """In place on float32: cap * tanh(x / cap)."""
+    _require_cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _check(load_library().bspec_tanh_softcap(x.data_ptr(), x.numel(), float(cap), _stream()), "tanh_softcap")
+    return x
+
+
+def gelu_erf_(x: torch.Tensor) -> torch.Tensor:
+    """In place: 0.5 x (1 + erf(x / sqrt 2))."""
+    _require_cuda(x)
+    assert x.is_contiguous()
+    _check(load_library().bspec_gelu_erf(x.data_ptr(), _dtype_code(x.dtype), x.numel(), _stream()), "gelu_erf")
+    return x
+
+
 GLU_FUSION = True
 GLU_GROUP = 8      # gate/up interleave of weights prepared for the fused epilogues: 8 gate rows, then their 8 up rows
 
@@ -277,16 +344,17 @@ def rope_kv_append(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: i
 
 
 def rope_inplace(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int,
-                 interleaved: bool = False) -> None:
-    """x: [n, H, hd] view whose last two dims are dense; rows may be strided.  ``inv_freq``: a
-    ``rope_frequency_table``."""
+                 interleaved: bool = False, magnitude: float = 1.0) -> None:
+    """x: [n, H, w] view whose last dim is dense; rows and heads may be strided, and the first ``rotary_dim`` numbers
+    of every head are rotated (a view of the rotated part of wider heads has a head stride larger than its width).
+    ``inv_freq``: a ``rope_frequency_table``.  ``magnitude`` multiplies cosine and sine."""
     _require_cuda(x, positions, inv_freq)
     n, H, hd = x.shape
-    assert x.stride(2) == 1 and x.stride(1) == hd and positions.dtype == torch.int32
+    assert x.stride(2) == 1 and hd >= rotary_dim and positions.dtype == torch.int32
     assert inv_freq.dtype == torch.float32 and inv_freq.shape == (2, rotary_dim // 2) and inv_freq.is_contiguous()
-    _check(load_library().bspec_rope_inplace(x.data_ptr(), _dtype_code(x.dtype), n, x.stride(0), H, hd,
+    _check(load_library().bspec_rope_inplace(x.data_ptr(), _dtype_code(x.dtype), n, x.stride(0), H, x.stride(1),
                                              inv_freq.data_ptr(), int(rotary_dim), int(bool(interleaved)),
-                                             positions.data_ptr(), _stream()), "rope_inplace")
+                                             positions.data_ptr(), float(magnitude), _stream()), "rope_inplace")
 
 
 # ---------------------------------------------------------------------------- attention
@@ -478,11 +546,13 @@ def check_status() -> None:
 
 
 _BOUNDS_REPORTS = ["bspec_bounds_report_elementwise", "bspec_bounds_report_gemm_tcgen05",
-                   "bspec_bounds_report_attention_generic", "bspec_bounds_report_attention_bf16"]
+                   "bspec_bounds_report_attention_generic", "bspec_bounds_report_attention_bf16",
+                   "bspec_bounds_report_latent"]
 BOUNDS_CODES = {101: "token id (embedding)", 102: "row (gather)", 103: "block-table slot (rotary + cache append)",
                 104: "page id (rotary + cache append)", 105: "block-table slot (q/k/v product's epilogue)",
                 106: "page id (q/k/v product's epilogue)", 107: "page id (attention over plain loads)",
-                108: "page id (bfloat16 attention over plain loads)"}
+                108: "page id (bfloat16 attention over plain loads)", 109: "block-table slot (latent entry append)",
+                110: "page id (latent entry append)", 111: "page id (latent attention over plain loads)"}
 
 
 def bounds_reports() -> list:
@@ -608,6 +678,155 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if out_dtype == x.dtype:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)
+
+
+def linear_batched(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x [B, M, K] (rows and batches may be strided, K dense) times w [B, N, K]^T -> [B, M, N] contiguous: one product
+    per head.  bfloat16 on the vendor library's batched product, float32 on this package's FFMA kernel."""
+    _require_cuda(x, w)
+    B, M, K = x.shape
+    N = w.shape[1]
+    assert w.shape == (B, N, K) and x.dtype == w.dtype and x.stride(2) == 1 and w.is_contiguous()
+    if x.dtype == torch.float32:
+        out = torch.empty((B, M, N), dtype=torch.float32, device=x.device)
+        _check(load_library().bspec_sgemm_tn_batched(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(1),
+                                                     K, N, x.stride(0), N * K, M * N, B, _stream()), "sgemm_tn_batched")
+        return out
+    return torch.bmm(x, w.transpose(1, 2))
+
+
+# ---------------------------------------------------------------------------- latent attention
+
+def latent_prepare(down: torch.Tensor, q_off: int, q_rank: int, kv_off: int, kv_rank: int, rot_dim: int,
+                   wq: torch.Tensor, wkv: torch.Tensor, eps: float, inv_freq: torch.Tensor, magnitude: float,
+                   positions: torch.Tensor, tok_entry: torch.Tensor, kv_indptr: torch.Tensor, kv_indices: torch.Tensor,
+                   cache: torch.Tensor, page_size: int, write_kv: bool = True) -> torch.Tensor:
+    """From the float32 rows of the down projections: the RMS-normalised query latent (returned, [n, q_rank] in the
+    cache's dtype) and the cache entry of every token, [normalised key/value latent | rotated key part], written
+    to the page of its position.  Rotation: adjacent pairs, ``magnitude`` on cosine and sine."""
+    _require_cuda(down, cache, positions)
+    n, ld = down.shape
+    assert down.dtype == torch.float32 and down.is_contiguous() and cache.is_contiguous()
+    assert wq.dtype == wkv.dtype and wq.numel() == q_rank and wkv.numel() == kv_rank
+    assert inv_freq.dtype == torch.float32 and inv_freq.shape == (2, rot_dim // 2) and inv_freq.is_contiguous()
+    assert q_off + q_rank <= ld and kv_off + kv_rank + rot_dim <= ld
+    cq = torch.empty((n, q_rank), dtype=cache.dtype, device=down.device)
+    _check(load_library().bspec_latent_prepare(
+        down.data_ptr(), n, ld, q_off, q_rank, kv_off, kv_rank, rot_dim, wq.data_ptr(), wkv.data_ptr(),
+        _dtype_code(wq.dtype), float(eps), inv_freq.data_ptr(), float(magnitude), positions.data_ptr(),
+        tok_entry.data_ptr(), kv_indptr.data_ptr(), kv_indices.data_ptr(), cq.data_ptr(), cache.data_ptr(),
+        _dtype_code(cache.dtype), int(page_size), int(bool(write_kv)), cache.shape[0], _stream()), "latent_prepare")
+    return cq
+
+
+FORCE_GENERIC_LATENT = False       # tests set this to compare the tensor-core kernel with the generic one
+
+
+def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, ctx, tables,
+                     n_heads: int, kv_rank: int, rot_dim: int, scale: float) -> None:
+    """Causal softmax attention in the latent space over the paged entries [c | kr].  ``q_lat`` [H, n, kv_rank] and
+    ``q_rot`` [n, H, rot_dim] (already rotated) are views with a dense last dim; ``out`` [H, n, kv_rank] receives
+    sum_j p_j c_j per head."""
+    _require_cuda(q_lat, q_rot, out, cache)
+    H, n, R = q_lat.shape
+    assert H == n_heads and R == kv_rank and q_rot.shape == (n, H, rot_dim) and out.shape == (H, n, R)
+    assert q_lat.stride(2) == 1 and q_rot.stride(2) == 1 and out.stride(2) == 1
+    assert q_lat.dtype == q_rot.dtype == out.dtype == cache.dtype and cache.is_contiguous()
+    lib = load_library()
+    if (q_lat.dtype == torch.bfloat16 and not FORCE_GENERIC_LATENT and hasattr(lib, "bspec_latent_attention_mma")
+            and latent_mma_supported(n_heads, kv_rank, rot_dim)):
+        _latent_attention_mma(lib, q_lat, q_rot, out, cache, ctx, tables, n_heads, kv_rank, rot_dim, scale)
+        return
+    _check(lib.bspec_latent_attention_generic(
+        q_lat.data_ptr(), q_lat.stride(1), q_lat.stride(0), q_rot.data_ptr(), q_rot.stride(0), q_rot.stride(1),
+        out.data_ptr(), out.stride(1), out.stride(0), cache.data_ptr(), _dtype_code(cache.dtype),
+        ctx.qo_indptr.data_ptr(), ctx.positions.data_ptr(), tables.kv_indptr.data_ptr(), tables.kv_indices.data_ptr(),
+        ctx.n_entries, ctx.max_q_len, n_heads, kv_rank, rot_dim, tables.page_size, float(scale), cache.shape[0],
+        _stream()), "latent_attention_generic")
+
+
+def latent_mma_supported(n_heads: int, kv_rank: int, rot_dim: int) -> bool:
+    return False
+
+
+def gate_heads(v: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, h*V + j] = v[h, t, j] * sigmoid(gate[t, h]).  ``v`` [H, n, V] with a dense last dim; ``gate`` a float32
+    view [n, H] of rows that may be wider."""
+    _require_cuda(v, gate, out)
+    H, n, V = v.shape
+    assert gate.dtype == torch.float32 and gate.shape == (n, H) and gate.stride(1) == 1 and v.stride(2) == 1
+    assert out.shape == (n, H * V) and out.is_contiguous() and out.dtype == v.dtype
+    _check(load_library().bspec_gate_heads(v.data_ptr(), v.stride(0), v.stride(1), gate.data_ptr(), gate.stride(0),
+                                           out.data_ptr(), _dtype_code(v.dtype), n, H, V, _stream()), "gate_heads")
+
+
+# ---------------------------------------------------------------------------- routed feed-forward
+
+MOE_LIBRARY_GROUPED = True       # bfloat16 steps with many rows per expert: the vendor library's grouped product
+MOE_LIBRARY_MIN_ROWS = 32        # ... from this many (token, choice) rows per expert on average
+
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], n_groups: int, keep: int,
+              top: int, scale: float):
+    """(expert ids int32 [n, top], weights float32 [n, top]) of every token; the rule is in ``csrc/moe.cu``."""
+    _require_cuda(h, router)
+    n, d = h.shape
+    E = router.shape[0]
+    assert router.shape == (E, d) and router.dtype == h.dtype and h.is_contiguous() and router.is_contiguous()
+    ids = torch.empty((n, top), dtype=torch.int32, device=h.device)
+    wts = torch.empty((n, top), dtype=torch.float32, device=h.device)
+    _check(load_library().bspec_moe_route(h.data_ptr(), _dtype_code(h.dtype), n, d, router.data_ptr(), _ptr(correction),
+                                          _dtype_code(correction.dtype) if correction is not None else F32, E,
+                                          int(n_groups), int(keep), int(top), float(scale), ids.data_ptr(),
+                                          wts.data_ptr(), _stream()), "moe_route")
+    return ids, wts
+
+
+def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
+                out_dtype: torch.dtype) -> torch.Tensor:
+    """sum_k wts[t, k] * Wdown[e] gelu(Wup[e] h[t]) with e = ids[t, k].  ``w_up`` [E, ff, d], ``w_down`` [E, d, ff].
+    The (token, choice) rows are sorted by expert on the device; no count is read on the host."""
+    _require_cuda(h, ids, wts, w_up, w_down)
+    lib = load_library()
+    n, d = h.shape
+    E, ff, _ = w_up.shape
+    top = ids.shape[1]
+    slots = n * top
+    assert w_up.shape == (E, ff, d) and w_down.shape == (E, d, ff) and w_up.is_contiguous() and w_down.is_contiguous()
+    assert h.is_contiguous() and ids.is_contiguous() and wts.is_contiguous() and h.dtype == w_up.dtype == w_down.dtype
+    dev, code = h.device, _dtype_code(h.dtype)
+    BM = 64 if slots >= 32 * E else 16
+    max_tiles = min(slots, slots // BM + E)
+    meta = torch.empty((2 * slots + E + 1 + 3 * max_tiles + 1,), dtype=torch.int32, device=dev)
+    perm, inv = meta[:slots], meta[slots:2 * slots]
+    offsets = meta[2 * slots:2 * slots + E + 1]
+    tiles = meta[2 * slots + E + 1:2 * slots + E + 1 + 3 * max_tiles]
+    n_tiles = meta[-1:]
+    _check(lib.bspec_moe_plan(ids.data_ptr(), slots, E, BM, perm.data_ptr(), inv.data_ptr(), offsets.data_ptr(),
+                              tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, _stream()), "moe_plan")
+    library = (MOE_LIBRARY_GROUPED and h.dtype == torch.bfloat16 and slots >= MOE_LIBRARY_MIN_ROWS * E
+               and d % 8 == 0 and ff % 8 == 0 and hasattr(torch, "_grouped_mm"))
+    if library:
+        rows = torch.empty((slots, d), dtype=h.dtype, device=dev)
+        _check(lib.bspec_moe_gather(h.data_ptr(), code, perm.data_ptr(), top, rows.data_ptr(), slots, d, _stream()),
+               "moe_gather")
+        ends = offsets[1:]
+        u = torch._grouped_mm(rows, w_up.transpose(1, 2), offs=ends)
+        gelu_erf_(u)
+        y = torch._grouped_mm(u, w_down.transpose(1, 2), offs=ends)
+    else:
+        u = torch.empty((slots, ff), dtype=h.dtype, device=dev)
+        y = torch.empty((slots, d), dtype=torch.float32, device=dev)
+        _check(lib.bspec_moe_grouped(h.data_ptr(), perm.data_ptr(), top, w_up.data_ptr(), u.data_ptr(), code, code, ff,
+                                     d, tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, BM, 1, _stream()),
+               "moe_grouped_up")
+        _check(lib.bspec_moe_grouped(u.data_ptr(), None, top, w_down.data_ptr(), y.data_ptr(), code, F32, d, ff,
+                                     tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, BM, 0, _stream()),
+               "moe_grouped_down")
+    out = torch.empty((n, d), dtype=out_dtype, device=dev)
+    _check(lib.bspec_moe_combine(y.data_ptr(), _dtype_code(y.dtype), inv.data_ptr(), wts.data_ptr(), top,
+                                 out.data_ptr(), _dtype_code(out_dtype), n, d, _stream()), "moe_combine")
+    return out
 
 
 # ---------------------------------------------------------------------------- sampling

@@ -1,7 +1,7 @@
 """Registry from an architecture's name to its model builder.
 
 The reference maps a *type* (standard / eagle / mtp) to a class
-(batchspec/models/__init__.py:101-142); here the key is ``architectures[0]`` of
+(batchspec/models/__init__.py:101-142); here the key is ``architectures[0]`` (or ``architecture``) of
 config.json and the value a function from that architecture's configuration to a
 ``ModelSpec``."""
 from __future__ import annotations
@@ -12,6 +12,7 @@ from ..parts.base import Runtime
 from .decoder import CacheNeed, DecoderModel, LayerCache
 from .llama import build_llama
 from .spec import LayerSpec, ModelSpec, RunEntry, prenorm_layer
+from .vabanex import build_vabanex
 
 MODEL_REGISTRY: Dict[str, Callable] = {}
 
@@ -28,6 +29,7 @@ def get_model(config, runtime: Runtime) -> DecoderModel:
 
 
 register_model("LlamaForCausalLM", build_llama)
+register_model("Vabanex", build_vabanex)
 
 __all__ = ["MODEL_REGISTRY", "register_model", "get_model", "DecoderModel", "LayerCache", "CacheNeed",
-           "ModelSpec", "LayerSpec", "RunEntry", "prenorm_layer", "build_llama"]
+           "ModelSpec", "LayerSpec", "RunEntry", "prenorm_layer", "build_llama", "build_vabanex"]

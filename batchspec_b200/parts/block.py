@@ -16,3 +16,13 @@ class PreNormBlock(Block):
         y = self.mixer.forward(a, ctx, cache)
         f = self.norm2.forward(resid, y)
         return resid, self.ffn.forward(f, ctx)
+
+
+@register_part(BLOCKS, "prenorm_mixer")
+class PreNormMixerBlock(Block):
+    """A pre-norm layer without a feed-forward: x' = x + mixer(norm1(x))."""
+    SLOTS = {"norm1": NORMS, "mixer": MIXERS}
+
+    def forward(self, resid, pending, ctx, cache):
+        a = self.norm1.forward(resid, pending)
+        return resid, self.mixer.forward(a, ctx, cache)

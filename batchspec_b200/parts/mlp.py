@@ -48,3 +48,33 @@ class SwiGLU(FeedForward):
                 ops.silu_mul(u, m)
         with bucket("mlp.down_proj"):
             return ops.linear(m, self.w2)
+
+
+@register_part(FEED_FORWARDS, "clamped_glu")
+class ClampedGLU(FeedForward):
+    """Gated feed-forward with clamped branches: g = min(Wgate x, limit), u = clamp(Wup x, -limit, limit),
+    y = g * sigmoid(alpha * g) * (u + 1), out = Wdown y.  No biases.  [gate; up] is one product."""
+    graph_safe = True
+
+    def __init__(self, runtime: Runtime, dim: int, intermediate: int, limit: float, alpha: float = 1.702):
+        self.runtime, self.dim, self.intermediate = runtime, int(dim), int(intermediate)
+        self.limit, self.alpha = float(limit), float(alpha)
+        self.w13 = self.w2 = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {"gate": ParamSpec((self.intermediate, self.dim)),
+                "up": ParamSpec((self.intermediate, self.dim)),
+                "down": ParamSpec((self.dim, self.intermediate))}
+
+    def bind(self, params):
+        self.w13 = torch.cat([params["gate"], params["up"]], dim=0).contiguous()
+        self.w2 = params["down"].contiguous()
+
+    def forward(self, x, ctx):
+        with bucket("mlp.gate_up_proj"):
+            u = ops.linear(x, self.w13)
+        m = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
+        with bucket("mlp.act"):
+            ops.clamped_glu(u, m, self.alpha, self.limit)
+        with bucket("mlp.down_proj"):
+            return ops.linear(m, self.w2)

@@ -1,0 +1,56 @@
+"""Routed feed-forward (mixture of experts) with sigmoid scores and group-limited choice.
+
+Per token, with h its normed input:  s = sigmoid(Wr h) in float32;  choice = s + correction;  the experts come in
+``n_groups`` equal groups of neighbours, a group's score is the sum of its two largest choices, and only experts of
+the best ``keep_groups`` groups can be chosen (the others count as minus infinity);  the ``top`` largest choices
+are taken;  their weights are s (without the correction) times ``scale``, not renormalised.
+Expert e is Wdown_e gelu(Wup_e h) with the exact (erf) GELU and no biases;  the output is the weighted sum.
+
+The experts' matrices are stacked at load ([E, ff, d] and [E, d, ff]); a step sorts its (token, choice) rows by
+expert on the device and runs one grouped product per projection over them (``ops.moe_experts``)."""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..kernels import ops
+from ..profiler import bucket
+from .base import FEED_FORWARDS, FeedForward, ParamSpec, Runtime, register_part
+
+
+@register_part(FEED_FORWARDS, "routed_gelu")
+class RoutedGelu(FeedForward):
+    graph_safe = True
+
+    def __init__(self, runtime: Runtime, dim: int, intermediate: int, n_experts: int, top: int, scale: float = 1.0,
+                 n_groups: int = 1, keep_groups: int = 1, correction: bool = True):
+        self.runtime, self.dim, self.intermediate = runtime, int(dim), int(intermediate)
+        self.n_experts, self.top, self.scale = int(n_experts), int(top), float(scale)
+        self.n_groups, self.keep_groups, self.correction = int(n_groups), int(keep_groups), bool(correction)
+        E, G = self.n_experts, self.n_groups
+        if not (0 < self.top <= E and G > 0 and E % G == 0 and 0 < self.keep_groups <= G
+                and self.keep_groups * (E // G) >= self.top):
+            raise ValueError(f"routing of {self.top} of {E} experts in {G} groups keeping {self.keep_groups} is not possible")
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        specs = {"router": ParamSpec((self.n_experts, self.dim))}
+        if self.correction:
+            specs["correction"] = ParamSpec((self.n_experts,), role="vector")
+        for e in range(self.n_experts):
+            specs[f"up{e}"] = ParamSpec((self.intermediate, self.dim))
+            specs[f"down{e}"] = ParamSpec((self.dim, self.intermediate))
+        return specs
+
+    def bind(self, params):
+        self.w_router = params["router"].contiguous()
+        self.b_correction = params["correction"].contiguous() if self.correction else None
+        self.w_up = torch.stack([params[f"up{e}"] for e in range(self.n_experts)]).contiguous()
+        self.w_down = torch.stack([params[f"down{e}"] for e in range(self.n_experts)]).contiguous()
+
+    def forward(self, x, ctx):
+        with bucket("mlp.router"):
+            ids, wts = ops.moe_route(x, self.w_router, self.b_correction, self.n_groups, self.keep_groups, self.top,
+                                     self.scale)
+        with bucket("mlp.experts"):
+            return ops.moe_experts(x, ids, wts, self.w_up, self.w_down, x.dtype)

@@ -30,3 +30,30 @@ class RMSNorm(Norm):
         with bucket("norm"):
             ops.add_rmsnorm(resid, delta, self.weight, self.eps, out)
         return out
+
+
+@register_part(NORMS, "layernorm")
+class LayerNorm(Norm):
+    """Layer norm with weight and bias: (x - mean) / sqrt(var + eps) * w + b, var the mean of the squared
+    deviations; float32 arithmetic, fused with the residual add that precedes it."""
+    graph_safe = True
+
+    def __init__(self, runtime: Runtime, dim: int, eps: float):
+        self.runtime, self.dim, self.eps = runtime, int(dim), float(eps)
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {"weight": ParamSpec((self.dim,), role="vector", init="ones_normal"),
+                "bias": ParamSpec((self.dim,), role="vector")}
+
+    def bind(self, params):
+        self.weight, self.bias = params["weight"], params["bias"]
+        if self.bias.dtype != self.weight.dtype:
+            self.bias = self.bias.to(self.weight.dtype)
+
+    def forward(self, resid, delta=None):
+        out = torch.empty(resid.shape, dtype=self.runtime.dtype, device=resid.device)
+        with bucket("norm"):
+            ops.add_layernorm(resid, delta, self.weight, self.bias, self.eps, out)
+        return out
