@@ -58,6 +58,11 @@ _SIGNATURES = {
     "bspec_latent_attention_generic": [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p,
                                        c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_void_p],
+    "bspec_latent_attention_mma_supported": [c_int, c_int],
+    "bspec_latent_attention_mma": [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p,
+                                   c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                   c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_longlong,
+                                   c_void_p],
     "bspec_gate_heads": [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "bspec_moe_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                         c_void_p, c_void_p, c_void_p],
@@ -126,7 +131,7 @@ def set_pdl(on: bool) -> None:
 
 _TRACE_SETTERS = ["bspec_trace_set_attention_tcgen05", "bspec_trace_set_elementwise", "bspec_trace_set_attention_generic", "bspec_trace_set_attention_bf16",
                   "bspec_trace_set_gemm_fp32", "bspec_trace_set_sampling", "bspec_trace_set_gemm_tcgen05", "bspec_trace_set_latent",
-                  "bspec_trace_set_moe"]
+                  "bspec_trace_set_moe", "bspec_trace_set_latent_mma"]
 TRACE_KERNEL_NAMES = {1: "embed", 2: "add_rmsnorm", 3: "gather_rows_add", 4: "silu_mul", 5: "rope_kv_append",
                       6: "rope_inplace", 7: "attn_generic", 8: "attn_decode", 9: "attn_prefill", 10: "sgemm",
                       11: "sample_threshold", 12: "sample_pick", 13: "sample_final", 14: "add_layernorm", 15: "clamped_glu",
@@ -547,12 +552,13 @@ def check_status() -> None:
 
 _BOUNDS_REPORTS = ["bspec_bounds_report_elementwise", "bspec_bounds_report_gemm_tcgen05",
                    "bspec_bounds_report_attention_generic", "bspec_bounds_report_attention_bf16",
-                   "bspec_bounds_report_latent"]
+                   "bspec_bounds_report_latent", "bspec_bounds_report_latent_mma"]
 BOUNDS_CODES = {101: "token id (embedding)", 102: "row (gather)", 103: "block-table slot (rotary + cache append)",
                 104: "page id (rotary + cache append)", 105: "block-table slot (q/k/v product's epilogue)",
                 106: "page id (q/k/v product's epilogue)", 107: "page id (attention over plain loads)",
                 108: "page id (bfloat16 attention over plain loads)", 109: "block-table slot (latent entry append)",
-                110: "page id (latent entry append)", 111: "page id (latent attention over plain loads)"}
+                110: "page id (latent entry append)", 111: "page id (latent attention over plain loads)",
+                112: "page id (latent attention on the tensor cores)"}
 
 
 def bounds_reports() -> list:
@@ -733,9 +739,28 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor
     assert q_lat.stride(2) == 1 and q_rot.stride(2) == 1 and out.stride(2) == 1
     assert q_lat.dtype == q_rot.dtype == out.dtype == cache.dtype and cache.is_contiguous()
     lib = load_library()
-    if (q_lat.dtype == torch.bfloat16 and not FORCE_GENERIC_LATENT and hasattr(lib, "bspec_latent_attention_mma")
-            and latent_mma_supported(n_heads, kv_rank, rot_dim)):
-        _latent_attention_mma(lib, q_lat, q_rot, out, cache, ctx, tables, n_heads, kv_rank, rot_dim, scale)
+    if (q_lat.dtype == torch.bfloat16 and not FORCE_GENERIC_LATENT and latent_mma_supported(kv_rank, rot_dim)
+            and out.stride(2) == 1 and out.stride(1) % 2 == 0 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0):
+        # Few rows and many entries (decode): the key tiles of a request are cut into shares for more CTAs.  The
+        # count depends on the step's shape alone (entries, longest portion, longest allowed request), so a
+        # captured step keeps it; shares that get no tile leave at once.
+        row_tiles = -(-(ctx.max_q_len * n_heads) // 64)
+        n_splits = 1
+        if ctx.max_q_len * n_heads <= 256:
+            n_splits = max(1, min(32, -(-2 * sm_count(q_lat.device) // (ctx.n_entries * row_tiles)),
+                                  -(-ctx.max_kv_len // 256)))
+        o_part = ml_part = None
+        if n_splits > 1:
+            o_part = torch.empty((n * H * n_splits * R,), dtype=torch.float32, device=q_lat.device)
+            ml_part = torch.empty((n * H * n_splits * 2,), dtype=torch.float32, device=q_lat.device)
+        _check(lib.bspec_latent_attention_mma(
+            q_lat.data_ptr(), q_lat.stride(1), q_lat.stride(0), q_rot.data_ptr(), q_rot.stride(0), q_rot.stride(1),
+            out.data_ptr(), out.stride(1), out.stride(0), cache.data_ptr(), ctx.qo_indptr.data_ptr(),
+            ctx.positions.data_ptr(), tables.kv_indptr.data_ptr(), tables.kv_indices.data_ptr(), ctx.n_entries, n,
+            ctx.max_q_len, n_heads, kv_rank, rot_dim, tables.page_size, float(scale), n_splits, _ptr(o_part),
+            _ptr(ml_part), cache.shape[0], _stream()), "latent_attention_mma")
+        if n_splits > 1:
+            count_launches(1)
         return
     _check(lib.bspec_latent_attention_generic(
         q_lat.data_ptr(), q_lat.stride(1), q_lat.stride(0), q_rot.data_ptr(), q_rot.stride(0), q_rot.stride(1),
@@ -745,8 +770,9 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor
         _stream()), "latent_attention_generic")
 
 
-def latent_mma_supported(n_heads: int, kv_rank: int, rot_dim: int) -> bool:
-    return False
+def latent_mma_supported(kv_rank: int, rot_dim: int) -> bool:
+    """Whether the tensor-core latent attention kernel takes these sizes (else the generic kernel runs)."""
+    return bool(load_library().bspec_latent_attention_mma_supported(int(kv_rank), int(rot_dim)))
 
 
 def gate_heads(v: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None:

@@ -195,7 +195,8 @@ def run_trace_subprocess(folder, dtype, steps, out_dir, max_tokens, extra_args=(
         if p.poll() is None:
             p.kill()
     out, pos = {}, {}
-    vocab = json.loads((Path(folder) / "config.json").read_text())["vocab_size"]
+    cfg_json = json.loads((Path(folder) / "config.json").read_text())
+    vocab = cfg_json["vocab_size"] if "vocab_size" in cfg_json else cfg_json["vocab"]
     for s in steps:
         n_want = sum(len(e.get("want", [])) for e in s["entries"])
         if n_want:
@@ -212,7 +213,7 @@ def run_trace_subprocess(folder, dtype, steps, out_dir, max_tokens, extra_args=(
     return out
 
 
-def compare_with_oracle(got, folder, requests, dtype_name, expect=None):
+def compare_with_oracle(got, folder, requests, dtype_name, expect=None, oracle=None, allow_over=0.0):
     """Every row against the plain implementation.  ``got`` has to hold exactly the rows ``expect`` (a set of
     (request, position); default: every position of every request), so a row that never came back fails the
     comparison instead of being skipped.  Returns the worst error and where it was."""
@@ -221,14 +222,20 @@ def compare_with_oracle(got, folder, requests, dtype_name, expect=None):
     assert set(got) == set(expect), (f"{len(set(expect) - set(got))} rows missing, {len(set(got) - set(expect))} "
                                      f"unexpected, e.g. {sorted(set(expect) ^ set(got), key=str)[:4]}")
     worst = (0.0, None)
+    over = rows = 0
     for rid, toks in requests.items():
-        ref = oracle_logits(folder, toks)
+        ref = (oracle or oracle_logits)(folder, toks)
         scale = np.abs(ref).max()
         for p in range(len(toks)):
             if (rid, p) not in expect:
                 continue
             err = float(np.abs(got[(rid, p)].astype(np.float64) - ref[p]).max() / scale)
+            rows += 1
+            over += err > TOL[dtype_name]
             if err > worst[0]:
                 worst = (err, (rid, p))
-    assert worst[0] <= TOL[dtype_name], f"worst relative error {worst[0]:.3e} at (request, position) {worst[1]}"
+    # ``allow_over``: the share of rows that may be beyond the tolerance (a model with a router, in bfloat16: a
+    # choice between two experts whose scores differ by less than the rounding falls either way)
+    assert over <= allow_over * rows, (f"{over} of {rows} rows beyond the tolerance, worst relative error "
+                                       f"{worst[0]:.3e} at (request, position) {worst[1]}")
     return worst
