@@ -40,10 +40,6 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-struct Smem {
-  __nv_bfloat16 *Q, *K, *Ph, *Pl;
-  float *S, *m, *l, *corr;
-};
 __host__ __device__ inline size_t smem_bytes(int D) {
   const int DP = D + 8;
   return (size_t)(BM + 2 * BN) * DP * 2 + (size_t)BM * (BN + 1) * 4 + 2 * (size_t)BM * (BN + 8) * 2 + 3 * BM * 4;
@@ -58,7 +54,8 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
                        const __nv_bfloat16* __restrict__ cache, const int* __restrict__ qo_indptr,
                        const int* __restrict__ positions, const int* __restrict__ kv_indptr,
                        const int* __restrict__ kv_indices, int H, int R, int P, int page_size, float scale,
-                       int n_splits, float* __restrict__ o_part, float* __restrict__ ml_part, long long n_pages) {
+                       int n_splits, float* __restrict__ o_part, float* __restrict__ ml_part, long long n_pages,
+                       const float* __restrict__ inv_freq, float magnitude) {
   bspec::pdl_prologue(43);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int D = R + P, DP = D + 8, PP = BN + 8, SP = BN + 1;
@@ -86,17 +83,41 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
   const int t_begin = split * per, t_end = min(n_tiles, t_begin + per);
   const int* table = kv_indices + kv_indptr[e];
 
-  // ---- queries: row r holds [ql | qr] of (token, head) = divmod(row0 + r, H); rows past the portion are zero
-  for (int idx = tid; idx < BM * D; idx += THREADS) {
-    const int r = idx / D, d = idx - r * D;
+  // ---- queries: row r holds [ql | qr] of (token, head) = divmod(row0 + r, H); rows past the portion are zero.
+  // With a frequency table the rotated part arrives unrotated and is rotated here (adjacent pairs, the angle in
+  // float64 from the two-float frequencies, cosine and sine times the magnitude), then rounded as a separate
+  // rotation kernel would have left it.
+  for (int idx = tid; idx < BM * (D / 2); idx += THREADS) {
+    const int r = idx / (D / 2), d = 2 * (idx - r * (D / 2));
     const long long row = row0 + r;
-    __nv_bfloat16 v = __float2bfloat16_rn(0.f);
+    float u = 0.f, v = 0.f;
     if (row < rows_total) {
       const long long t = q_begin + row / H;
       const int h = (int)(row % H);
-      v = d < R ? ql[t * ql_row + h * ql_head + d] : qr[t * qr_row + h * qr_head + (d - R)];
+      if (d < R) {
+        const __nv_bfloat16* src = ql + t * ql_row + h * ql_head + d;
+        u = __bfloat162float(src[0]);
+        v = __bfloat162float(src[1]);
+      } else {
+        const __nv_bfloat16* src = qr + t * qr_row + h * qr_head + (d - R);
+        u = __bfloat162float(src[0]);
+        v = __bfloat162float(src[1]);
+        if (inv_freq != nullptr) {
+          const int j = (d - R) / 2, half = P / 2;
+          const double f = (double)inv_freq[j] + (double)inv_freq[half + j];
+          double ang = (double)positions[t] * f;
+          ang -= 6.283185307179586476925286766559 * rint(ang * 0.15915494309189533576888376337251);
+          float sn, cs;
+          sincosf((float)ang, &sn, &cs);
+          sn *= magnitude;
+          cs *= magnitude;
+          const float ru = u * cs - v * sn, rv = v * cs + u * sn;
+          u = ru;
+          v = rv;
+        }
+      }
     }
-    Qs[(size_t)r * DP + d] = v;
+    *reinterpret_cast<__nv_bfloat162*>(Qs + (size_t)r * DP + d) = __floats2bfloat162_rn(u, v);
   }
   if (tid < BM) {
     row_m[tid] = -INFINITY;
@@ -303,7 +324,8 @@ BSPEC_API int bspec_latent_attention_mma(const void* ql, long long ql_row, long 
                                          const int* positions, const int* kv_indptr, const int* kv_indices,
                                          int n_entries, int n_tokens, int max_q_len, int H, int R, int P,
                                          int page_size, float scale, int n_splits, float* o_part, float* ml_part,
-                                         long long n_pages, cudaStream_t stream) {
+                                         long long n_pages, const float* inv_freq, float magnitude,
+                                         cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return 0;
   if (!bspec_latent_attention_mma_supported(R, P) || n_splits < 1 || (n_splits > 1 && (!o_part || !ml_part)))
     return (int)cudaErrorInvalidValue;
@@ -318,7 +340,7 @@ BSPEC_API int bspec_latent_attention_mma(const void* ql, long long ql_row, long 
     BSPEC_LAUNCH((latent_attn_mma_kernel<N>), grid, THREADS, smem, stream, (const __nv_bfloat16*)ql, ql_row, ql_head, \
                  (const __nv_bfloat16*)qr, qr_row, qr_head, (__nv_bfloat16*)out, o_row, o_head,                      \
                  (const __nv_bfloat16*)cache, qo_indptr, positions, kv_indptr, kv_indices, H, R, P, page_size,       \
-                 scale, n_splits, o_part, ml_part, n_pages);                                                         \
+                 scale, n_splits, o_part, ml_part, n_pages, inv_freq, magnitude);                                    \
   } while (0)
   if (ntw <= 8) LM(8); else if (ntw <= 16) LM(16); else LM(32);
 #undef LM

@@ -62,7 +62,7 @@ _SIGNATURES = {
     "bspec_latent_attention_mma": [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p,
                                    c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                    c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_longlong,
-                                   c_void_p],
+                                   c_void_p, c_float, c_void_p],
     "bspec_gate_heads": [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "bspec_moe_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                         c_void_p, c_void_p, c_void_p],
@@ -729,10 +729,12 @@ FORCE_GENERIC_LATENT = False       # tests set this to compare the tensor-core k
 
 
 def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, ctx, tables,
-                     n_heads: int, kv_rank: int, rot_dim: int, scale: float) -> None:
+                     n_heads: int, kv_rank: int, rot_dim: int, scale: float, rotate=None) -> None:
     """Causal softmax attention in the latent space over the paged entries [c | kr].  ``q_lat`` [H, n, kv_rank] and
-    ``q_rot`` [n, H, rot_dim] (already rotated) are views with a dense last dim; ``out`` [H, n, kv_rank] receives
-    sum_j p_j c_j per head."""
+    ``q_rot`` [n, H, rot_dim] are views with a dense last dim; ``out`` [H, n, kv_rank] receives sum_j p_j c_j per
+    head.  ``rotate`` None: ``q_rot`` is already rotated.  ``rotate`` = (``rope_frequency_table``, magnitude):
+    it is not, and is rotated by adjacent pairs on the way, inside the tensor-core kernel as it loads the queries,
+    or in place by the rotation kernel before the generic one."""
     _require_cuda(q_lat, q_rot, out, cache)
     H, n, R = q_lat.shape
     assert H == n_heads and R == kv_rank and q_rot.shape == (n, H, rot_dim) and out.shape == (H, n, R)
@@ -758,10 +760,13 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor
             out.data_ptr(), out.stride(1), out.stride(0), cache.data_ptr(), ctx.qo_indptr.data_ptr(),
             ctx.positions.data_ptr(), tables.kv_indptr.data_ptr(), tables.kv_indices.data_ptr(), ctx.n_entries, n,
             ctx.max_q_len, n_heads, kv_rank, rot_dim, tables.page_size, float(scale), n_splits, _ptr(o_part),
-            _ptr(ml_part), cache.shape[0], _stream()), "latent_attention_mma")
+            _ptr(ml_part), cache.shape[0], rotate[0].data_ptr() if rotate else None,
+            float(rotate[1]) if rotate else 1.0, _stream()), "latent_attention_mma")
         if n_splits > 1:
             count_launches(1)
         return
+    if rotate:
+        rope_inplace(q_rot, ctx.positions, rotate[0], rot_dim, True, rotate[1])
     _check(lib.bspec_latent_attention_generic(
         q_lat.data_ptr(), q_lat.stride(1), q_lat.stride(0), q_rot.data_ptr(), q_rot.stride(0), q_rot.stride(1),
         out.data_ptr(), out.stride(1), out.stride(0), cache.data_ptr(), _dtype_code(cache.dtype),

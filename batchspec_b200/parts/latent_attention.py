@@ -14,8 +14,8 @@ are never formed: since q_h . (Wuk_h c) = (Wuk_h^T q_h) . c, the unrotated query
 up-projection is applied to its attended latent afterwards.  The step's launch sequence:
 
     one product for [Wdq; Wdkv; Wg] (float32 out) -> latent_prepare (both RMS norms in float32, rotation of kr,
-    cache append) -> Wuq -> rotation of the queries' rotated parts -> per-head Wuk^T -> latent attention ->
-    per-head Wuv -> gate and regroup -> Wo
+    cache append) -> Wuq -> per-head Wuk^T -> latent attention (which rotates the queries' rotated parts as it
+    loads them) -> per-head Wuv -> gate and regroup -> Wo
 """
 from __future__ import annotations
 
@@ -89,14 +89,13 @@ class LatentAttention(Mixer):
                                     tables.kv_indices, cache.kv, tables.page_size, write_kv=cache.owner)
         with bucket("attn.q_proj"):
             q = ops.linear(cq, self.w_uq).view(n, H, dh + P)
-        q_rot = q[:, :, dh:]
-        with bucket("attn.rope"):
-            pos.apply(q_rot, None, ctx)
+        q_rot = q[:, :, dh:]                      # rotated on its way into the attention kernel
         with bucket("attn.absorb"):
             q_lat = ops.linear_batched(q[:, :, :dh].transpose(0, 1), self.w_uk_t)          # [H, n, R]
         o_lat = torch.empty((H, n, R), dtype=x.dtype, device=x.device)
         with bucket("attn.compute"):
-            ops.latent_attention(q_lat, q_rot, o_lat, cache.kv, ctx, tables, H, R, P, self.scale)
+            ops.latent_attention(q_lat, q_rot, o_lat, cache.kv, ctx, tables, H, R, P, self.scale,
+                                 rotate=(pos.inv_freq, pos.magnitude))
         with bucket("attn.v_proj"):
             v = ops.linear_batched(o_lat, self.w_uv)                                        # [H, n, v_dim]
         heads = torch.empty((n, H * self.v_dim), dtype=x.dtype, device=x.device)

@@ -291,6 +291,141 @@ def run_cfg5(pk):
     return out
 
 
+# ---- a second design beside the headline model (``--design vabanex``); the default workload does not run this
+
+VABANEX_SIZES = {
+    # width, heads, unrotated / rotated / value size per head, ranks, experts (count, chosen, ff, groups, kept), dense ff
+    "w2048": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, q_rank=768, kv_rank=512,
+                  experts=64, top=6, expert_ff=1408, groups=8, keep=4, dense_ff=8448, kv_heads=4),
+    "w4096": dict(width=4096, heads=32, dim=128, rot=64, vdim=128, q_rank=1536, kv_rank=512,
+                  experts=64, top=8, expert_ff=2048, groups=8, keep=4, dense_ff=14336, kv_heads=8),
+}
+
+
+def vabanex_config_json(z, layers, vocab=32000):
+    mixer = dict(heads=z["heads"], dim=z["dim"], rot_dim=z["rot"], vdim=z["vdim"], q_rank=z["q_rank"],
+                 kv_rank=z["kv_rank"], scale=(z["dim"] + z["rot"]) ** -0.5,
+                 rot=dict(base=10000.0, dims=z["rot"], scaling=dict(factor=40.0, original=4096, fast=32.0, slow=1.0)))
+    moe = dict(kind="moe", expert=dict(ff=z["expert_ff"]),
+               router=dict(experts=z["experts"], top=z["top"], scale=2.5, groups=dict(count=z["groups"], keep=z["keep"])))
+    dense = dict(kind="dense", ff=z["dense_ff"], limit=7.0)
+    return dict(architecture="Vabanex", vocab=vocab, width=z["width"], embedding=dict(scale=1.0), norm=dict(eps=1e-5),
+                logit_softcap=30.0,
+                layers=[dict(type="latent_attention", mixer=mixer, mlp=dense if i == 0 else moe) for i in range(layers)])
+
+
+def llama_config_json(z, layers, vocab=32000):
+    """The closest existing model at equal size: same width, depth, heads and vocabulary; its feed-forward has the
+    width of the first layer's dense one."""
+    return dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_act="silu", vocab_size=vocab,
+                hidden_size=z["width"], num_hidden_layers=layers, num_attention_heads=z["heads"],
+                num_key_value_heads=z["kv_heads"], head_dim=128, intermediate_size=z["dense_ff"], rms_norm_eps=1e-5,
+                rope_theta=500000.0, rope_scaling=None, max_position_embeddings=131072, tie_word_embeddings=False)
+
+
+def run_buckets(eng, cfg, n_tokens, page_size=16):
+    """Device time of every part of one prompt step of ``n_tokens`` (CUDA events around each part's launches)."""
+    import torch
+    from batchspec_b200.engine import StepEntry
+    from batchspec_b200.profiler import Profiler, register_active_profiler, release_active_profiler
+    eng.setup_caches(max_batch_size=1, max_seq_length=n_tokens + 16, page_size=page_size)
+    p = prompts_for(1, cfg.vocab_size, 2)[0][:n_tokens]
+    prof = Profiler(warmup_runs=0, output_dir="/tmp/bspec_prof")
+    register_active_profiler(prof)
+    try:
+        prof.begin_run()
+        for it in range(3):
+            eng.admit("p")
+            with prof.step_timing_ctx():
+                eng.step([StepEntry("p", p, want=(n_tokens - 1,))])
+            eng.release("p")
+        buckets = prof.steps[-1]["buckets"]
+    finally:
+        release_active_profiler()
+    return {k: round(v, 3) for k, v in sorted(buckets.items())}
+
+
+def latent_attention_alone(z, pk, iters=20):
+    """The latent attention kernel by itself: a prompt of 4,096 tokens (FLOP/s against the measured product peak:
+    scores over rank + rotated numbers, values over the rank) and a decode step of 64 requests x 4,096 entries
+    (bytes of entries read once against the measured copy rate; 1.1 GB of entries, beyond the L2)."""
+    import torch
+    from types import SimpleNamespace
+    from batchspec_b200.kernels import ops
+    dev = "cuda:0"
+    Hh, R, Pd, ps = z["heads"], z["kv_rank"], z["rot"], 16
+    out = {}
+    for name, q_lens, ctx_len in (("prompt_4096", [4096], 4096), ("decode_64x4096", [1] * 64, 4096)):
+        n, B = sum(q_lens), len(q_lens)
+        pages_per = -(-ctx_len // ps)
+        cache = torch.randn(B * pages_per, 1, ps * (R + Pd), device=dev).bfloat16()
+        ql = torch.randn(Hh, n, R, device=dev).bfloat16()
+        qr = torch.randn(n, Hh, Pd, device=dev).bfloat16()
+        o = torch.empty(Hh, n, R, device=dev, dtype=torch.bfloat16)
+        qo = torch.tensor([0] + list(__import__("itertools").accumulate(q_lens)), dtype=torch.int32, device=dev)
+        pos = torch.cat([torch.arange(ctx_len - q, ctx_len) for q in q_lens]).to(dev, torch.int32)
+        ent = torch.cat([torch.full((q,), i) for i, q in enumerate(q_lens)]).to(dev, torch.int32)
+        ctx = SimpleNamespace(qo_indptr=qo, positions=pos, tok_entry=ent, n_entries=B, n_tokens=n, max_q_len=max(q_lens),
+                              max_kv_len=ctx_len, extras={})
+        tables = SimpleNamespace(kv_indptr=torch.arange(B + 1, dtype=torch.int32, device=dev) * pages_per,
+                                 kv_indices=torch.randperm(B * pages_per, device=dev).to(torch.int32), page_size=ps)
+        run = lambda: ops.latent_attention(ql, qr, o, cache, ctx, tables, Hh, R, Pd, 0.05)
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(iters):
+            run()
+        e.record()
+        torch.cuda.synchronize()
+        ms = s.elapsed_time(e) / iters
+        if name.startswith("prompt"):
+            flops = 2.0 * Hh * (R + Pd + R) * ctx_len * (ctx_len + 1) / 2
+            out[name] = dict(ms=round(ms, 4), tflops=round(flops / ms / 1e9, 1),
+                             frac_of_measured=round(flops / ms / 1e9 / pk["bf16_tflops"], 4))
+        else:
+            nbytes = B * ctx_len * (R + Pd) * 2
+            out[name] = dict(ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1),
+                             frac_of_measured=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
+    return out
+
+
+def run_design(a) -> int:
+    """Prompt and decode throughput of the Vabanex design at layer sizes of real models (random weights, bfloat16)
+    beside the Llama model of equal size, with the device time of every part of a prompt step and the latent
+    attention kernel by itself.  One JSON line."""
+    import torch
+    from batchspec_b200.config import config_from_json_dict
+    from batchspec_b200.engine import Engine
+    pk = peaks()
+    layers = a.layers or 4
+    out = {"design": a.design, "layers": layers, "dtype": "bf16", "data": "synthetic", "prompt_len": PROMPT_LEN,
+           "peaks": pk["source"], "sizes": {}}
+    for size, z in VABANEX_SIZES.items():
+        rec = {}
+        for label, cj in (("vabanex", vabanex_config_json(z, layers)), ("llama", llama_config_json(z, layers))):
+            cfg = config_from_json_dict(cj)
+            eng = Engine(dtype="bfloat16", device="cuda:0")
+            eng.load_model(config=cfg, random_seed=0, draw_on_device=True)
+            eng.setup_sampling_params(temperature=0.0)
+            r = {"prefill_ms": round(run_prefill(eng, cfg), 3)}
+            r["prefill_tok_s"] = round(PROMPT_LEN / (r["prefill_ms"] * 1e-3), 1)
+            for b in (8, 64):
+                ms, launches = run_decode(eng, cfg, b, a.steps, max(a.warmup, 3))
+                r[f"decode_b{b}_ms"] = round(ms, 4)
+                r[f"decode_b{b}_tok_s"] = round(b * 1000.0 / ms, 1)
+                r[f"decode_b{b}_launches_per_step"] = launches // a.steps
+            r["prompt_step_parts_ms"] = run_buckets(eng, cfg, PROMPT_LEN)
+            rec[label] = r
+            del eng
+            torch.cuda.empty_cache()
+        rec["latent_attention_alone"] = latent_attention_alone(z, pk)
+        out["sizes"][size] = rec
+    print(json.dumps(out))
+    return 0
+
+
 def reference_arm(a) -> int:
     """``--impl reference``: the unmodified reference through its own ``StandardEngine.generate`` (see
     baseline/reference_arm.py) on the same workload: batch, 2,048-token prompts, greedy decode steps.  If it cannot
@@ -350,9 +485,13 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (no prefill, b1, b64, e2e)")
     ap.add_argument("--skip-workloads", action="store_true",
                     help="leave out e2e at batch 64 and the 3B / long-context workloads (about a minute)")
+    ap.add_argument("--design", default=None, choices=["vabanex"],
+                    help="instead of the headline workload: this design at real layer sizes beside the Llama model of equal size")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm(a)
+    if a.design:
+        return run_design(a)
     if a.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2

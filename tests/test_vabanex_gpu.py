@@ -243,6 +243,41 @@ def test_latent_attention(ops, dtype, shape, generic):
     assert (got - want).abs().max() <= (2e-5 if dtype == torch.float32 else 2.5e-2)
 
 
+@pytest.mark.parametrize("generic", [False, True])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_latent_attention_rotates_the_queries_on_the_way(ops, dtype, generic):
+    """Given a frequency table, the kernels take the queries' rotated parts unrotated (a view inside wider heads)
+    and give what rotating them first and attending then gives."""
+    Hh, R, Pd, ps, dh = 16, 64, 32, 16, 24
+    f, mag = P.yarn_frequencies(dict(base=5000.0, dims=Pd, scaling=dict(factor=4.0, original=64, fast=16.0, slow=1.0)))
+    table = ops.rope_frequency_table(f, DEV)
+    q_lens, kv_lens = [40, 1, 3], [300, 77, 3]
+    n = sum(q_lens)
+    g = torch.Generator(device=DEV).manual_seed(17)
+    ql = torch.randn(Hh, n, R, device=DEV, generator=g).to(dtype)
+    q = torch.randn(n, Hh, dh + Pd, device=DEV, generator=g).to(dtype)
+    pages_per = [-(-L // ps) for L in kv_lens]
+    cache = torch.randn(sum(pages_per), 1, ps * (R + Pd), device=DEV, generator=g).to(dtype)
+    qo = [0] + list(np.cumsum(q_lens))
+    pos = torch.cat([torch.arange(L - x, L) for x, L in zip(q_lens, kv_lens)]).to(DEV, torch.int32)
+    ent = torch.cat([torch.full((x,), i) for i, x in enumerate(q_lens)]).to(DEV, torch.int32)
+    ctx = SimpleNamespace(qo_indptr=torch.tensor(qo, dtype=torch.int32, device=DEV), positions=pos, tok_entry=ent,
+                          n_entries=3, n_tokens=n, max_q_len=max(q_lens), max_kv_len=max(kv_lens), extras={})
+    tables = SimpleNamespace(kv_indptr=torch.tensor([0] + list(np.cumsum(pages_per)), dtype=torch.int32, device=DEV),
+                             kv_indices=torch.arange(sum(pages_per), dtype=torch.int32, device=DEV), page_size=ps)
+    first = q.clone()
+    ops.rope_inplace(first[:, :, dh:], pos, table, Pd, True, mag)
+    want = torch.empty(Hh, n, R, device=DEV, dtype=dtype)
+    got = torch.empty(Hh, n, R, device=DEV, dtype=dtype)
+    ops.FORCE_GENERIC_LATENT = generic
+    try:
+        ops.latent_attention(ql, first[:, :, dh:], want, cache, ctx, tables, Hh, R, Pd, 0.1)
+        ops.latent_attention(ql, q.clone()[:, :, dh:], got, cache, ctx, tables, Hh, R, Pd, 0.1, rotate=(table, mag))
+    finally:
+        ops.FORCE_GENERIC_LATENT = False
+    assert torch.equal(got, want)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("key", [0, 15, 16, 511, 512, 1023, 1500])
 def test_one_far_entry_among_hundreds_is_found(ops, dtype, key):
