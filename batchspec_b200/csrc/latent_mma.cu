@@ -1,12 +1,16 @@
 // Latent attention in bfloat16 on the tensor cores (mma.sync m16n8k16, float32 accumulation), prompt portions and
 // decoded tokens alike.  All heads of a request read the same cache entries [c | kr] (R + P numbers), so the rows
-// of a tile are (token, head) pairs: row = token * H + head, 64 rows per CTA, and one pass over the request's
-// entries serves every head.  Per tile of 32 entries:
+// of a tile are (token, head) pairs: row = token * H + head, 16 * RG rows per CTA (RG row groups of 16: 64 rows for
+// prompt portions, 16 or 32 for decoded tokens of models with up to 16 or 32 heads), and one pass over the request's
+// entries serves every head.  A CTA is RG x CH warps: warp (rg, ch) owns 16 rows, 32 / CH keys of every score tile
+// and R / CH columns of the output.  Per tile of 32 entries:
 //
 //   S = Q K^T over all R + P numbers (the entry is the key), scaled, causal mask, to shared memory in float32;
 //   online softmax in float32, four threads per row; the weights are left as TWO bfloat16 numbers, the rounded
 //   weight and the rounding's remainder, so that the product with the values carries them to 2^-17;
-//   O += P_hi V + P_lo V with V the first R numbers of the same tile, each warp owning 16 rows and half of R.
+//   O += P_hi V + P_lo V with V the first R numbers of the same tile.
+// The warps of a row group meet at a barrier of their own between these phases (the row groups drift apart, so
+// one's softmax runs under another's products); the whole CTA meets once per tile, when the next tile has landed.
 //
 // Entries arrive by cp.async, two tiles in flight.  With n_splits > 1 (decode: few rows, many entries) CTA z takes
 // the z-th share of the key tiles and leaves (max, sum, unnormalised output) for the join kernel, which adds the
@@ -17,7 +21,7 @@ using namespace bspec;
 
 namespace {
 
-constexpr int BM = 64, BN = 32, THREADS = 256;
+constexpr int BN = 32;
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
@@ -30,6 +34,10 @@ __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
 }
+__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n"
+               : "=r"(r[0]), "=r"(r[1]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
 __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
@@ -40,14 +48,15 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-__host__ __device__ inline size_t smem_bytes(int D) {
+__host__ __device__ inline size_t smem_bytes(int D, int BM) {
   const int DP = D + 8;
-  return (size_t)(BM + 2 * BN) * DP * 2 + (size_t)BM * (BN + 1) * 4 + 2 * (size_t)BM * (BN + 8) * 2 + 3 * BM * 4;
+  return (size_t)(BM + 2 * BN) * DP * 2 + (size_t)BM * (BN + 8) * 4 + 2 * (size_t)BM * (BN + 8) * 2 + 3 * BM * 4;
 }
 
-// NT: n-tiles (of 8 columns) of the output that one warp may own: R / 16 <= NT.
-template <int NT>
-__global__ void __launch_bounds__(THREADS)
+// RG row groups x CH column groups of warps; NT: n-tiles (of 8 columns) of the output one warp may own,
+// R / (8 CH) <= NT.
+template <int RG, int CH, int NT>
+__global__ void __launch_bounds__(32 * RG * CH)
 latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, long long ql_head,
                        const __nv_bfloat16* __restrict__ qr, long long qr_row, long long qr_head,
                        __nv_bfloat16* __restrict__ out, long long o_row, long long o_head,
@@ -56,9 +65,13 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
                        const int* __restrict__ kv_indices, int H, int R, int P, int page_size, float scale,
                        int n_splits, float* __restrict__ o_part, float* __restrict__ ml_part, long long n_pages,
                        const float* __restrict__ inv_freq, float magnitude) {
+  constexpr int BM = 16 * RG, THREADS = 32 * RG * CH;
+  constexpr int KW = BN / CH;                     // keys of a score tile per warp: 16 or 8
+  constexpr int TPR = 2 * CH, KPT = BN / TPR;     // softmax: threads per row, keys per thread
   bspec::pdl_prologue(43);
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int D = R + P, DP = D + 8, PP = BN + 8, SP = BN + 1;
+  const int D = R + P, DP = D + 8;
+  constexpr int PP = BN + 8, SP = BN + 8;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* Ks = Qs + (size_t)BM * DP;
   float* Ss = reinterpret_cast<float*>(Ks + (size_t)2 * BN * DP);
@@ -74,7 +87,7 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
   const long long row0 = (long long)blockIdx.x * BM;
   if (row0 >= rows_total) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int rg = warp & 3, ch = warp >> 2;
+  const int rg = warp % RG, ch = warp / RG;
   const int pos0 = positions[q_begin];
   const int last_tok = (int)min((long long)q_len - 1, (row0 + BM - 1) / H);
   const int max_pos = pos0 + last_tok;
@@ -124,105 +137,153 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
     row_l[tid] = 0.f;
   }
 
+  // A tile's entries are dealt to the warps, one entry at a time; the lanes copy its 16-byte pieces.  The page
+  // of an entry is looked up once per entry (a shift when the page size is a power of two).
   const int chunks = D / 8;                       // 16-byte pieces of an entry
+  const int ps_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
   auto load_tile = [&](int tile, int buf) {
     __nv_bfloat16* dst = Ks + (size_t)buf * BN * DP;
-    for (int c = tid; c < BN * chunks; c += THREADS) {
-      const int k = c / chunks, part = c - k * chunks;
+    for (int k = warp; k < BN; k += RG * CH) {
       const int key = tile * BN + k;
       bool valid = key <= max_pos;
       const __nv_bfloat16* src = cache;
       if (valid) {
-        const int page = table[key / page_size];
+        const int slot = ps_shift >= 0 ? key >> ps_shift : key / page_size;
+        const int page = table[slot];
         valid = bspec::in_range(page, n_pages, 112);
-        if (valid) src = cache + ((size_t)page * page_size + key % page_size) * D + part * 8;
+        if (valid) src = cache + ((size_t)page * page_size + (key - slot * page_size)) * D;
       }
-      cp_async16(dst + (size_t)k * DP + part * 8, src, valid);
+      __nv_bfloat16* d = dst + (size_t)k * DP;
+      for (int part = lane; part < chunks; part += 32) cp_async16(d + part * 8, valid ? src + part * 8 : src, valid);
     }
+  };
+  auto group_barrier = [&]() {
+    if (RG == 1) __syncthreads();
+    else asm volatile("bar.sync %0, %1;" ::"r"(1 + rg), "r"(32 * CH) : "memory");
   };
 
   float o[NT][4];
 #pragma unroll
   for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-  const int ntw = R / 16;                         // n-tiles this warp owns
-  const int col0 = ch * (R / 2);                  // its first output column
+  const int ntw = R / (8 * CH);                   // n-tiles this warp owns
+  const int col0 = ch * (R / CH);                 // its first output column
   const int mat = lane >> 3, r8 = lane & 7;
   const int qrow = lane >> 2, qcol = 2 * (lane & 3);
+  // this thread's softmax row: the row group's 32 CH threads, TPR per row
+  const int tg = ch * 32 + lane;
+  const int srow = 16 * rg + tg / TPR, spart = tg % TPR;
+  // the last key each of this thread's two score rows may see (-1: the row is past the portion)
+  int row_pos[2];
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const long long row = row0 + 16 * rg + qrow + 8 * half;
+    row_pos[half] = row < rows_total ? pos0 + (int)(row / H) : -1;
+  }
 
   if (t_begin < t_end) load_tile(t_begin, 0);
   cp_async_commit();
   for (int tile = t_begin; tile < t_end; ++tile) {
     const int buf = (tile - t_begin) & 1;
+    cp_async_wait<0>();
+    __syncthreads();                              // the tile is here, and everybody is done with the tile before
     if (tile + 1 < t_end) load_tile(tile + 1, buf ^ 1);
     cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
     const __nv_bfloat16* Kt = Ks + (size_t)buf * BN * DP;
-    // ---- S: this warp's 16 rows x 16 keys
+    // ---- S: this warp's 16 rows x KW keys, two accumulator sets over alternating k steps
     {
-      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-      for (int ks = 0; ks < D / 16; ++ks) {
-        uint32_t a[4], b[4];
-        ldsm_x4(a, Qs + (size_t)(16 * rg + 8 * (mat & 1) + r8) * DP + 16 * ks + 8 * (mat >> 1));
-        ldsm_x4(b, Kt + (size_t)(16 * ch + 8 * (mat >> 1) + r8) * DP + 16 * ks + 8 * (mat & 1));
-        mma_bf16(s[0], a, b[0], b[1]);
-        mma_bf16(s[1], a, b[2], b[3]);
-      }
+      constexpr int NS = KW / 8;
+      float s[2][NS][4];
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
+      for (int x = 0; x < 2; ++x)
+#pragma unroll
+        for (int y = 0; y < NS; ++y) s[x][y][0] = s[x][y][1] = s[x][y][2] = s[x][y][3] = 0.f;
+      const __nv_bfloat16* qa = Qs + (size_t)(16 * rg + 8 * (mat & 1) + r8) * DP + 8 * (mat >> 1);
+      const __nv_bfloat16* kb = KW == 16 ? Kt + (size_t)(KW * ch + 8 * (mat >> 1) + r8) * DP + 8 * (mat & 1)
+                                         : Kt + (size_t)(KW * ch + r8) * DP + 8 * (mat & 1);
+      const int nks = D / 16;
+      auto step = [&](float (&acc)[NS][4], int ks) {
+        uint32_t a[4];
+        ldsm_x4(a, qa + 16 * ks);
+        if (KW == 16) {
+          uint32_t b[4];
+          ldsm_x4(b, kb + 16 * ks);
+          mma_bf16(acc[0], a, b[0], b[1]);
+          mma_bf16(acc[NS - 1], a, b[2], b[3]);
+        } else {
+          uint32_t b[2];
+          ldsm_x2(b, kb + 16 * ks);
+          mma_bf16(acc[0], a, b[0], b[1]);
+        }
+      };
+      int ks = 0;
+      for (; ks + 1 < nks; ks += 2) {
+        step(s[0], ks);
+        step(s[1], ks + 1);
+      }
+      if (ks < nks) step(s[0], ks);
+#pragma unroll
+      for (int nt = 0; nt < NS; ++nt)
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           const int r = 16 * rg + qrow + 8 * half;
-          const long long row = row0 + r;
-          const int pos = pos0 + (int)min((long long)q_len - 1, row / H);
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            const int c = 16 * ch + 8 * nt + qcol + j;
-            const int key = tile * BN + c;
-            Ss[r * SP + c] = (row < rows_total && key <= pos) ? s[nt][2 * half + j] * scale : -INFINITY;
-          }
+          const int c = KW * ch + 8 * nt + qcol;
+          const int key = tile * BN + c;
+          float2 v;
+          v.x = key <= row_pos[half] ? (s[0][nt][2 * half] + s[1][nt][2 * half]) * scale : -INFINITY;
+          v.y = key + 1 <= row_pos[half] ? (s[0][nt][2 * half + 1] + s[1][nt][2 * half + 1]) * scale : -INFINITY;
+          *reinterpret_cast<float2*>(Ss + r * SP + c) = v;
         }
     }
-    __syncthreads();
-    // ---- softmax: four threads per row, eight keys each
+    group_barrier();
+    // ---- softmax: TPR threads per row, KPT keys each
     {
-      const int r = tid >> 2, part = tid & 3;
-      float v[8];
+      float v[KPT];
       float mx = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        v[j] = Ss[r * SP + 8 * part + j];
-        mx = fmaxf(mx, v[j]);
+      for (int j = 0; j < KPT; j += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(Ss + srow * SP + KPT * spart + j);
+        v[j] = x.x; v[j + 1] = x.y; v[j + 2] = x.z; v[j + 3] = x.w;
       }
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-      const float m_old = row_m[r], l_old = row_l[r];
+#pragma unroll
+      for (int j = 0; j < KPT; ++j) mx = fmaxf(mx, v[j]);
+#pragma unroll
+      for (int x = 1; x < TPR; x <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, x));
+      const float m_old = row_m[srow], l_old = row_l[srow];
       const float m_new = fmaxf(m_old, mx);
       float sum = 0.f;
+      __align__(16) __nv_bfloat16 hi[KPT], lo[KPT];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float p = m_new == -INFINITY ? 0.f : expf(v[j] - m_new);
+      for (int j = 0; j < KPT; ++j) {
+        const float p = m_new == -INFINITY ? 0.f : __expf(v[j] - m_new);
         sum += p;
-        const __nv_bfloat16 hi = __float2bfloat16_rn(p);
-        Ph[r * PP + 8 * part + j] = hi;
-        Pl[r * PP + 8 * part + j] = __float2bfloat16_rn(p - __bfloat162float(hi));
+        hi[j] = __float2bfloat16_rn(p);
+        lo[j] = __float2bfloat16_rn(p - __bfloat162float(hi[j]));
       }
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      if (part == 0) {
-        const float corr = m_new == -INFINITY ? 1.f : expf(m_old - m_new);
-        row_m[r] = m_new;
-        row_l[r] = l_old * corr + sum;
-        row_c[r] = corr;
+      if (KPT == 8) {
+        *reinterpret_cast<uint4*>(Ph + srow * PP + KPT * spart) = *reinterpret_cast<const uint4*>(hi);
+        *reinterpret_cast<uint4*>(Pl + srow * PP + KPT * spart) = *reinterpret_cast<const uint4*>(lo);
+      } else {
+        *reinterpret_cast<uint2*>(Ph + srow * PP + KPT * spart) = *reinterpret_cast<const uint2*>(hi);
+        *reinterpret_cast<uint2*>(Pl + srow * PP + KPT * spart) = *reinterpret_cast<const uint2*>(lo);
+      }
+#pragma unroll
+      for (int x = 1; x < TPR; x <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, x);
+      if (spart == 0) {
+        const float corr = m_new == -INFINITY ? 1.f : __expf(m_old - m_new);
+        row_m[srow] = m_new;
+        row_l[srow] = l_old * corr + sum;
+        row_c[srow] = corr;
       }
     }
-    __syncthreads();
+    group_barrier();
     // ---- O = O * corr + P V over this warp's columns
     {
       const float c_lo = row_c[16 * rg + qrow], c_hi = row_c[16 * rg + qrow + 8];
+      if (!__all_sync(0xffffffffu, c_lo == 1.f && c_hi == 1.f)) {      // some row's maximum moved
 #pragma unroll
-      for (int i = 0; i < NT; ++i) {
-        o[i][0] *= c_lo; o[i][1] *= c_lo; o[i][2] *= c_hi; o[i][3] *= c_hi;
+        for (int i = 0; i < NT; ++i) {
+          o[i][0] *= c_lo; o[i][1] *= c_lo; o[i][2] *= c_hi; o[i][3] *= c_hi;
+        }
       }
 #pragma unroll
       for (int kk = 0; kk < BN / 16; ++kk) {
@@ -244,7 +305,6 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
         }
       }
     }
-    __syncthreads();
   }
   cp_async_wait<0>();
   __syncthreads();          // row_m / row_l of the init (no tiles) or of the last tile, for every warp
@@ -315,7 +375,16 @@ __global__ void latent_attn_join_kernel(const float* __restrict__ o_part, const 
 // 1 if the tensor-core kernel takes these sizes (ranks and rotated part multiples of 16, latent at most 512,
 // the tile fits shared memory), else 0.
 BSPEC_API int bspec_latent_attention_mma_supported(int R, int P) {
-  return (R > 0 && R % 16 == 0 && P >= 16 && P % 16 == 0 && R <= 512 && smem_bytes(R + P) <= 220 * 1024) ? 1 : 0;
+  return (R > 0 && R % 16 == 0 && P >= 16 && P % 16 == 0 && R <= 512 && smem_bytes(R + P, 64) <= 220 * 1024) ? 1 : 0;
+}
+
+// Rows per CTA for a step whose longest portion has max_q_len tokens: 16 or 32 when every request's (token, head)
+// rows fit (decoded tokens of models with few heads; needs a latent that is a multiple of 32), else 64.
+BSPEC_API int bspec_latent_attention_mma_rows(int max_q_len, int H, int R) {
+  const long long rows = (long long)max_q_len * H;
+  if (R % 32 == 0 && rows <= 16) return 16;
+  if (R % 32 == 0 && rows <= 32) return 32;
+  return 64;
 }
 
 BSPEC_API int bspec_latent_attention_mma(const void* ql, long long ql_row, long long ql_head, const void* qr,
@@ -329,20 +398,27 @@ BSPEC_API int bspec_latent_attention_mma(const void* ql, long long ql_row, long 
   if (n_entries <= 0 || max_q_len <= 0) return 0;
   if (!bspec_latent_attention_mma_supported(R, P) || n_splits < 1 || (n_splits > 1 && (!o_part || !ml_part)))
     return (int)cudaErrorInvalidValue;
+  const int BM = bspec_latent_attention_mma_rows(max_q_len, H, R);
   const long long row_tiles = ((long long)max_q_len * H + BM - 1) / BM;
   if (row_tiles > 2147483647ll || n_entries > 65535 || n_splits > 65535) return (int)cudaErrorInvalidConfiguration;
   dim3 grid((unsigned)row_tiles, n_entries, n_splits);
-  const size_t smem = smem_bytes(R + P);
-  const int ntw = R / 16;
-#define LM(N)                                                                                                        \
+  const size_t smem = smem_bytes(R + P, BM);
+#define LM(RG, CH, N)                                                                                                \
   do {                                                                                                               \
-    cudaFuncSetAttribute(latent_attn_mma_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
-    BSPEC_LAUNCH((latent_attn_mma_kernel<N>), grid, THREADS, smem, stream, (const __nv_bfloat16*)ql, ql_row, ql_head, \
-                 (const __nv_bfloat16*)qr, qr_row, qr_head, (__nv_bfloat16*)out, o_row, o_head,                      \
+    cudaFuncSetAttribute(latent_attn_mma_kernel<RG, CH, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    BSPEC_LAUNCH((latent_attn_mma_kernel<RG, CH, N>), grid, 32 * RG * CH, smem, stream, (const __nv_bfloat16*)ql,    \
+                 ql_row, ql_head, (const __nv_bfloat16*)qr, qr_row, qr_head, (__nv_bfloat16*)out, o_row, o_head,     \
                  (const __nv_bfloat16*)cache, qo_indptr, positions, kv_indptr, kv_indices, H, R, P, page_size,       \
                  scale, n_splits, o_part, ml_part, n_pages, inv_freq, magnitude);                                    \
   } while (0)
-  if (ntw <= 8) LM(8); else if (ntw <= 16) LM(16); else LM(32);
+  if (BM == 64) {
+    const int ntw = R / 16;
+    if (ntw <= 8) LM(4, 2, 8); else if (ntw <= 16) LM(4, 2, 16); else LM(4, 2, 32);
+  } else {
+    const int ntw = R / 32;
+    if (BM == 16) { if (ntw <= 4) LM(1, 4, 4); else if (ntw <= 8) LM(1, 4, 8); else LM(1, 4, 16); }
+    else { if (ntw <= 4) LM(2, 4, 4); else if (ntw <= 8) LM(2, 4, 8); else LM(2, 4, 16); }
+  }
 #undef LM
   int err = BSPEC_LAUNCH_CHECK();
   if (err != 0 || n_splits == 1) return err;

@@ -47,43 +47,53 @@ moe_route_kernel(const T* __restrict__ h, int d, const T* __restrict__ wr, const
     }
   }
   __syncthreads();
-  if (threadIdx.x != 0) return;
+  if (warp != 0) return;
+  // The choice is made by warp 0: every lane scans its share of the candidates, a shuffle tree finds the best
+  // (the larger value, the lower index among equals), lane 0 marks it as taken (NaN).
+  auto best_of = [&](const float* v, int n) -> int {
+    float bv = 0.f;
+    int bi = 0x7fffffff;
+    for (int i = lane; i < n; i += 32) {
+      const float x = v[i];
+      if (!isnan(x) && (bi == 0x7fffffff || x > bv)) { bv = x; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+    }
+    return bi;
+  };
   if (G > 1 && keep < G) {
     const int per = E / G;
-    // group scores into the start of hs (no longer needed)
-    for (int g = 0; g < G; ++g) {
-      float a = -INFINITY, b = -INFINITY;       // the two largest
+    for (int g = lane; g < G; g += 32) {          // group scores into the start of hs (no longer needed)
+      float a = -INFINITY, b = -INFINITY;         // the two largest
       for (int j = 0; j < per; ++j) {
         const float v = ch[g * per + j];
         if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
       }
       hs[g] = per > 1 ? a + b : a;
     }
-    // keep the best `keep` groups: mark them by taking their score out
+    __syncwarp();
     for (int k = 0; k < keep; ++k) {
-      int best = -1;
-      float bv = -INFINITY;
-      for (int g = 0; g < G; ++g) {
-        const float v = hs[g];
-        if (!isnan(v) && (best < 0 || v > bv)) { best = g; bv = v; }
-      }
-      if (best >= 0) hs[best] = NAN;            // NaN marks a kept group
+      const int best = best_of(hs, G);
+      if (lane == 0 && best != 0x7fffffff) hs[best] = NAN;      // NaN marks a kept group
+      __syncwarp();
     }
-    for (int g = 0; g < G; ++g)
-      if (!isnan(hs[g]))
-        for (int j = 0; j < per; ++j) ch[g * per + j] = -INFINITY;
+    for (int i = lane; i < E; i += 32)
+      if (!isnan(hs[i / per])) ch[i] = -INFINITY;
+    __syncwarp();
   }
   for (int k = 0; k < top; ++k) {
-    int best = 0;
-    float bv = -INFINITY;
-    bool found = false;
-    for (int e = 0; e < E; ++e) {
-      const float v = ch[e];
-      if (!isnan(v) && (!found || v > bv)) { best = e; bv = v; found = true; }
+    int best = best_of(ch, E);
+    if (best == 0x7fffffff) best = 0;
+    if (lane == 0) {
+      ids[(size_t)t * top + k] = best;
+      wts[(size_t)t * top + k] = sc[best] * scale;
+      ch[best] = NAN;                             // taken
     }
-    ids[(size_t)t * top + k] = best;
-    wts[(size_t)t * top + k] = sc[best] * scale;
-    ch[best] = NAN;                             // taken
+    __syncwarp();
   }
 }
 
@@ -199,6 +209,77 @@ moe_grouped_kernel(const T* __restrict__ A, const int* __restrict__ perm, int to
   }
 }
 
+// The same product for tiles of at most 8 rows (decode-sized steps: a handful of rows per expert), bfloat16, bound
+// by the read of the experts' weights.  The tile's rows wait in shared memory; every warp owns 8 output columns,
+// 4 at a time; its lanes stride over K in 16-byte pieces of the weight rows (four loads in flight per lane) and a
+// shuffle tree adds the lanes' sums.  A value depends on its row and column alone.
+__device__ __forceinline__ float dot8(const uint4& w, const uint4& a, float acc) {
+  const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&w);
+  const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x = __bfloat1622float2(w2[i]), y = __bfloat1622float2(a2[i]);
+    acc = fmaf(x.x, y.x, acc);
+    acc = fmaf(x.y, y.y, acc);
+  }
+  return acc;
+}
+
+template <typename TO, bool GELU>
+__global__ void __launch_bounds__(256)
+moe_skinny_kernel(const __nv_bfloat16* __restrict__ A, const int* __restrict__ perm, int top,
+                  const __nv_bfloat16* __restrict__ W, TO* __restrict__ C, int N, int K, const int* __restrict__ tiles,
+                  const int* __restrict__ n_tiles) {
+  bspec::pdl_prologue(55);
+  constexpr int RMAX = 8;
+  if ((int)blockIdx.y >= *n_tiles) return;
+  extern __shared__ uint4 As4[];                  // [rows][K / 8]
+  const int e = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int K8 = K / 8;
+  for (int idx = tid; idx < rows * K8; idx += 256) {
+    const int r = idx / K8, c = idx - r * K8;
+    const int src = perm != nullptr ? perm[row0 + r] / top : row0 + r;
+    As4[idx] = reinterpret_cast<const uint4*>(A + (size_t)src * K)[c];
+  }
+  __syncthreads();
+  const __nv_bfloat16* We = W + (size_t)e * N * K;
+  const int n_base = blockIdx.x * 64 + warp * 8;
+#pragma unroll 1
+  for (int g = 0; g < 2; ++g) {
+    const int n0 = n_base + 4 * g;
+    if (n0 >= N) break;
+    const uint4* wrow[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) wrow[j] = reinterpret_cast<const uint4*>(We + (size_t)min(n0 + j, N - 1) * K);
+    float acc[4][RMAX];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int r = 0; r < RMAX; ++r) acc[j][r] = 0.f;
+    for (int c = lane; c < K8; c += 32) {
+      uint4 w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = __ldg(wrow[j] + c);
+#pragma unroll
+      for (int r = 0; r < RMAX; ++r)
+        if (r < rows) {
+          const uint4 a = As4[r * K8 + c];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[j][r] = dot8(w[j], a, acc[j][r]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int r = 0; r < RMAX; ++r)
+        if (r < rows) {
+          const float v = warp_sum(acc[j][r]);
+          if (lane == 0 && n0 + j < N) C[(size_t)(row0 + r) * N + n0 + j] = from_f32<TO>(GELU ? gelu_erf(v) : v);
+        }
+  }
+}
+
 // sorted[r, :] = h[perm[r] / top, :]
 template <typename T>
 __global__ void moe_gather_kernel(const T* __restrict__ h, const int* __restrict__ perm, int top, T* __restrict__ out,
@@ -246,7 +327,7 @@ BSPEC_API int bspec_moe_route(const void* h, int dtype, int n, int d, const void
 BSPEC_API int bspec_moe_plan(const int* ids, int slots, int E, int BM, int* perm, int* inv, int* offsets, int* tiles,
                              int* n_tiles, int max_tiles, cudaStream_t stream) {
   if (slots <= 0) return 0;
-  if (E <= 0 || E > MAX_EXPERTS || (BM != 16 && BM != 64)) return (int)cudaErrorInvalidValue;
+  if (E <= 0 || E > MAX_EXPERTS || (BM != 8 && BM != 16 && BM != 64)) return (int)cudaErrorInvalidValue;
   BSPEC_LAUNCH((moe_plan_kernel), 1, 1024, 0, stream, ids, slots, E, BM, perm, inv, offsets, tiles, n_tiles, max_tiles);
   return BSPEC_LAUNCH_CHECK();
 }
@@ -266,6 +347,29 @@ BSPEC_API int bspec_moe_grouped(const void* A, const int* perm, int top, const v
   else LB(__nv_bfloat16, __nv_bfloat16);
 #undef LB
 #undef LK
+  return BSPEC_LAUNCH_CHECK();
+}
+
+// Tiles of at most 8 rows (a plan made with BM = 8), bfloat16 operands, K a multiple of 8.
+BSPEC_API int bspec_moe_skinny(const void* A, const int* perm, int top, const void* W, void* C, int out_dtype, int N,
+                               int K, const int* tiles, const int* n_tiles, int max_tiles, int gelu,
+                               cudaStream_t stream) {
+  if (max_tiles <= 0 || N <= 0) return 0;
+  if (K % 8 != 0 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
+    return (int)cudaErrorInvalidValue;
+  dim3 grid((N + 63) / 64, max_tiles);
+  if (grid.y > 65535) return (int)cudaErrorInvalidConfiguration;
+  const size_t smem = (size_t)8 * K * 2;
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+#define LS(TO, G)                                                                                                   \
+  do {                                                                                                              \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_skinny_kernel<TO, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    BSPEC_LAUNCH((moe_skinny_kernel<TO, G>), grid, 256, smem, stream, (const __nv_bfloat16*)A, perm, top,           \
+                 (const __nv_bfloat16*)W, (TO*)C, N, K, tiles, n_tiles);                                            \
+  } while (0)
+  if (out_dtype == BSPEC_F32) { if (gelu) LS(float, true); else LS(float, false); }
+  else { if (gelu) LS(__nv_bfloat16, true); else LS(__nv_bfloat16, false); }
+#undef LS
   return BSPEC_LAUNCH_CHECK();
 }
 

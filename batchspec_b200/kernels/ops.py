@@ -59,6 +59,7 @@ _SIGNATURES = {
                                        c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_void_p],
     "bspec_latent_attention_mma_supported": [c_int, c_int],
+    "bspec_latent_attention_mma_rows": [c_int, c_int, c_int],
     "bspec_latent_attention_mma": [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p,
                                    c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                    c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_longlong,
@@ -69,6 +70,8 @@ _SIGNATURES = {
     "bspec_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "bspec_moe_grouped": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                           c_int, c_int, c_int, c_void_p],
+    "bspec_moe_skinny": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                         c_int, c_void_p],
     "bspec_moe_gather": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
     "bspec_moe_combine": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
     "bspec_sgemm_tn_batched": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
@@ -137,7 +140,7 @@ TRACE_KERNEL_NAMES = {1: "embed", 2: "add_rmsnorm", 3: "gather_rows_add", 4: "si
                       11: "sample_threshold", 12: "sample_pick", 13: "sample_final", 14: "add_layernorm", 15: "clamped_glu",
                       16: "gelu_erf", 17: "tanh_softcap", 20: "gemm_tcgen05", 30: "attn_prefill_tc", 40: "latent_prepare",
                       41: "latent_attn_generic", 42: "gate_heads", 43: "latent_attn_mma", 44: "latent_attn_join",
-                      50: "moe_route", 51: "moe_plan", 52: "moe_grouped", 53: "moe_gather", 54: "moe_combine"}
+                      50: "moe_route", 51: "moe_plan", 52: "moe_grouped", 53: "moe_gather", 54: "moe_combine", 55: "moe_skinny"}
 
 
 def set_trace(buf: Optional[torch.Tensor], count: Optional[torch.Tensor]) -> None:
@@ -746,11 +749,14 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor
         # Few rows and many entries (decode): the key tiles of a request are cut into shares for more CTAs.  The
         # count depends on the step's shape alone (entries, longest portion, longest allowed request), so a
         # captured step keeps it; shares that get no tile leave at once.
-        row_tiles = -(-(ctx.max_q_len * n_heads) // 64)
+        rows = lib.bspec_latent_attention_mma_rows(ctx.max_q_len, n_heads, kv_rank)       # rows of a CTA's tile
+        row_tiles = -(-(ctx.max_q_len * n_heads) // rows)
         n_splits = 1
         if ctx.max_q_len * n_heads <= 256:
-            n_splits = max(1, min(32, -(-2 * sm_count(q_lat.device) // (ctx.n_entries * row_tiles)),
-                                  -(-ctx.max_kv_len // 256)))
+            # as many shares as fill the CTAs that are resident at once (one wave), at least 128 keys each
+            smem = (rows + 64) * (kv_rank + rot_dim + 8) * 2 + rows * 330
+            slots = sm_count(q_lat.device) * max(1, min(4, (220 * 1024) // smem))
+            n_splits = max(1, min(64, slots // (ctx.n_entries * row_tiles), -(-ctx.max_kv_len // 128)))
         o_part = ml_part = None
         if n_splits > 1:
             o_part = torch.empty((n * H * n_splits * R,), dtype=torch.float32, device=q_lat.device)
@@ -795,6 +801,7 @@ def gate_heads(v: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None:
 
 MOE_LIBRARY_GROUPED = True       # bfloat16 steps with many rows per expert: the vendor library's grouped product
 MOE_LIBRARY_MIN_ROWS = 32        # ... from this many (token, choice) rows per expert on average
+MOE_SKINNY = True                # bfloat16 steps with fewer rows per expert: the weight-streaming kernel
 
 
 def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], n_groups: int, keep: int,
@@ -826,7 +833,12 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: tor
     assert w_up.shape == (E, ff, d) and w_down.shape == (E, d, ff) and w_up.is_contiguous() and w_down.is_contiguous()
     assert h.is_contiguous() and ids.is_contiguous() and wts.is_contiguous() and h.dtype == w_up.dtype == w_down.dtype
     dev, code = h.device, _dtype_code(h.dtype)
-    BM = 64 if slots >= 32 * E else 16
+    library = (MOE_LIBRARY_GROUPED and h.dtype == torch.bfloat16 and slots >= MOE_LIBRARY_MIN_ROWS * E
+               and d % 8 == 0 and ff % 8 == 0 and hasattr(torch, "_grouped_mm"))
+    # few rows per expert in bfloat16: tiles of 8 rows on the kernel that streams the experts' weights
+    skinny = (not library and MOE_SKINNY and h.dtype == torch.bfloat16 and slots < 32 * E and d % 8 == 0
+              and ff % 8 == 0 and 16 * max(d, ff) <= 200 * 1024)
+    BM = 8 if skinny else (64 if slots >= 32 * E else 16)
     max_tiles = min(slots, slots // BM + E)
     meta = torch.empty((2 * slots + E + 1 + 3 * max_tiles + 1,), dtype=torch.int32, device=dev)
     perm, inv = meta[:slots], meta[slots:2 * slots]
@@ -835,8 +847,6 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: tor
     n_tiles = meta[-1:]
     _check(lib.bspec_moe_plan(ids.data_ptr(), slots, E, BM, perm.data_ptr(), inv.data_ptr(), offsets.data_ptr(),
                               tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, _stream()), "moe_plan")
-    library = (MOE_LIBRARY_GROUPED and h.dtype == torch.bfloat16 and slots >= MOE_LIBRARY_MIN_ROWS * E
-               and d % 8 == 0 and ff % 8 == 0 and hasattr(torch, "_grouped_mm"))
     if library:
         rows = torch.empty((slots, d), dtype=h.dtype, device=dev)
         _check(lib.bspec_moe_gather(h.data_ptr(), code, perm.data_ptr(), top, rows.data_ptr(), slots, d, _stream()),
@@ -845,6 +855,13 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: tor
         u = torch._grouped_mm(rows, w_up.transpose(1, 2), offs=ends)
         gelu_erf_(u)
         y = torch._grouped_mm(u, w_down.transpose(1, 2), offs=ends)
+    elif skinny:
+        u = torch.empty((slots, ff), dtype=h.dtype, device=dev)
+        y = torch.empty((slots, d), dtype=torch.float32, device=dev)
+        _check(lib.bspec_moe_skinny(h.data_ptr(), perm.data_ptr(), top, w_up.data_ptr(), u.data_ptr(), code, ff, d,
+                                    tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, 1, _stream()), "moe_skinny_up")
+        _check(lib.bspec_moe_skinny(u.data_ptr(), None, top, w_down.data_ptr(), y.data_ptr(), F32, d, ff,
+                                    tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, 0, _stream()), "moe_skinny_down")
     else:
         u = torch.empty((slots, ff), dtype=h.dtype, device=dev)
         y = torch.empty((slots, d), dtype=torch.float32, device=dev)

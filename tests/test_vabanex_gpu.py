@@ -354,7 +354,8 @@ def test_router_groups_and_negative_choices(ops, dtype, E, G, keep, top):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n,E,top,d,ff", [(1, 4, 2, 32, 24), (9, 6, 3, 100, 36), (300, 8, 4, 64, 40), (40, 16, 1, 72, 8)])
+@pytest.mark.parametrize("n,E,top,d,ff", [(1, 4, 2, 32, 24), (9, 6, 3, 100, 36), (300, 8, 4, 64, 40), (40, 16, 1, 72, 8),
+                                          (8, 64, 6, 512, 136), (64, 32, 4, 264, 1032)])
 def test_routed_experts(ops, dtype, n, E, top, d, ff):
     g = torch.Generator(device=DEV).manual_seed(n)
     h = torch.randn(n, d, device=DEV, generator=g).to(dtype)
@@ -364,13 +365,13 @@ def test_routed_experts(ops, dtype, n, E, top, d, ff):
     if n > 8:
         ids[3:8] = ids[3]                          # some experts with many rows, some perhaps with none
     wts = torch.rand(n, top, device=DEV, generator=g) + 0.1
-    for library in (False, True):
-        was = ops.MOE_LIBRARY_MIN_ROWS
-        ops.MOE_LIBRARY_MIN_ROWS = 0 if library else 1 << 30
+    for library, skinny in ((False, True), (False, False), (True, True)):     # the three kinds of grouped product
+        was = ops.MOE_LIBRARY_MIN_ROWS, ops.MOE_SKINNY
+        ops.MOE_LIBRARY_MIN_ROWS, ops.MOE_SKINNY = (0 if library else 1 << 30), skinny
         try:
             out = ops.moe_experts(h, ids, wts, w_up, w_down, dtype)
         finally:
-            ops.MOE_LIBRARY_MIN_ROWS = was
+            ops.MOE_LIBRARY_MIN_ROWS, ops.MOE_SKINNY = was
         want = torch.zeros(n, d, dtype=torch.float64)
         for t in range(n):
             for k in range(top):
