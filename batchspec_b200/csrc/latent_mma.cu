@@ -30,17 +30,19 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool vali
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+// ldmatrix on 32-bit shared-space addresses (formed once per kernel, advanced by byte offsets)
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t a) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
-__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void* p) {
+__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], uint32_t a) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n"
-               : "=r"(r[0]), "=r"(r[1]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+               : "=r"(r[0]), "=r"(r[1]) : "r"(a));
 }
-__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t a) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -65,7 +67,7 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
                        const int* __restrict__ kv_indices, int H, int R, int P, int page_size, float scale,
                        int n_splits, float* __restrict__ o_part, float* __restrict__ ml_part, long long n_pages,
                        const float* __restrict__ inv_freq, float magnitude) {
-  constexpr int BM = 16 * RG, THREADS = 32 * RG * CH;
+  constexpr int BM = 16 * RG;
   constexpr int KW = BN / CH;                     // keys of a score tile per warp: 16 or 8
   constexpr int TPR = 2 * CH, KPT = BN / TPR;     // softmax: threads per row, keys per thread
   bspec::pdl_prologue(43);
@@ -100,37 +102,37 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
   // With a frequency table the rotated part arrives unrotated and is rotated here (adjacent pairs, the angle in
   // float64 from the two-float frequencies, cosine and sine times the magnitude), then rounded as a separate
   // rotation kernel would have left it.
-  for (int idx = tid; idx < BM * (D / 2); idx += THREADS) {
-    const int r = idx / (D / 2), d = 2 * (idx - r * (D / 2));
+  for (int r = warp; r < BM; r += RG * CH) {      // a warp per row: its token and head are found once
     const long long row = row0 + r;
-    float u = 0.f, v = 0.f;
-    if (row < rows_total) {
-      const long long t = q_begin + row / H;
-      const int h = (int)(row % H);
-      if (d < R) {
-        const __nv_bfloat16* src = ql + t * ql_row + h * ql_head + d;
-        u = __bfloat162float(src[0]);
-        v = __bfloat162float(src[1]);
-      } else {
-        const __nv_bfloat16* src = qr + t * qr_row + h * qr_head + (d - R);
-        u = __bfloat162float(src[0]);
-        v = __bfloat162float(src[1]);
-        if (inv_freq != nullptr) {
-          const int j = (d - R) / 2, half = P / 2;
-          const double f = (double)inv_freq[j] + (double)inv_freq[half + j];
-          double ang = (double)positions[t] * f;
-          ang -= 6.283185307179586476925286766559 * rint(ang * 0.15915494309189533576888376337251);
-          float sn, cs;
-          sincosf((float)ang, &sn, &cs);
-          sn *= magnitude;
-          cs *= magnitude;
-          const float ru = u * cs - v * sn, rv = v * cs + u * sn;
-          u = ru;
-          v = rv;
-        }
-      }
+    const bool live = row < rows_total;
+    const int tq = live ? (int)((unsigned)row / (unsigned)H) : 0;          // rows_total fits 32 bits (checked at launch)
+    const int h = live ? (int)((unsigned)row - (unsigned)tq * (unsigned)H) : 0;
+    const long long t = q_begin + tq;
+    const __nv_bfloat16* src_l = ql + t * ql_row + h * ql_head;
+    const __nv_bfloat16* src_r = qr + t * qr_row + h * qr_head;
+    __nv_bfloat16* dst = Qs + (size_t)r * DP;
+    for (int d = 2 * lane; d < R; d += 64) {
+      const float u = live ? __bfloat162float(src_l[d]) : 0.f, v = live ? __bfloat162float(src_l[d + 1]) : 0.f;
+      *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(u, v);
     }
-    *reinterpret_cast<__nv_bfloat162*>(Qs + (size_t)r * DP + d) = __floats2bfloat162_rn(u, v);
+    const int pos = live ? positions[t] : 0;
+    for (int d = 2 * lane; d < P; d += 64) {
+      float u = live ? __bfloat162float(src_r[d]) : 0.f, v = live ? __bfloat162float(src_r[d + 1]) : 0.f;
+      if (inv_freq != nullptr && live) {
+        const int j = d / 2, half = P / 2;
+        const double f = (double)inv_freq[j] + (double)inv_freq[half + j];
+        double ang = (double)pos * f;
+        ang -= 6.283185307179586476925286766559 * rint(ang * 0.15915494309189533576888376337251);
+        float sn, cs;
+        sincosf((float)ang, &sn, &cs);
+        sn *= magnitude;
+        cs *= magnitude;
+        const float ru = u * cs - v * sn, rv = v * cs + u * sn;
+        u = ru;
+        v = rv;
+      }
+      *reinterpret_cast<__nv_bfloat162*>(dst + R + d) = __floats2bfloat162_rn(u, v);
+    }
   }
   if (tid < BM) {
     row_m[tid] = -INFINITY;
@@ -141,20 +143,30 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
   // of an entry is looked up once per entry (a shift when the page size is a power of two).
   const int chunks = D / 8;                       // 16-byte pieces of an entry
   const int ps_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
-  auto load_tile = [&](int tile, int buf) {
-    __nv_bfloat16* dst = Ks + (size_t)buf * BN * DP;
-    for (int k = warp; k < BN; k += RG * CH) {
-      const int key = tile * BN + k;
-      bool valid = key <= max_pos;
-      const __nv_bfloat16* src = cache;
-      if (valid) {
+  // Lane j of a warp looks up the page of the warp's j-th entry of a tile; the lookup for a tile is made one
+  // tile ahead of its copies, so that its latency passes under the products in between.
+  constexpr int NW = RG * CH, KPW = BN / NW;      // warps; entries of a tile per warp
+  auto lookup = [&](int tile) -> long long {      // element offset of the lane's entry in the cache, -1: none
+    long long off = -1;
+    if (lane < KPW && tile < t_end) {
+      const int key = tile * BN + warp + lane * NW;
+      if (key <= max_pos) {
         const int slot = ps_shift >= 0 ? key >> ps_shift : key / page_size;
         const int page = table[slot];
-        valid = bspec::in_range(page, n_pages, 112);
-        if (valid) src = cache + ((size_t)page * page_size + (key - slot * page_size)) * D;
+        if (bspec::in_range(page, n_pages, 112)) off = ((long long)page * page_size + (key - slot * page_size)) * D;
       }
-      __nv_bfloat16* d = dst + (size_t)k * DP;
-      for (int part = lane; part < chunks; part += 32) cp_async16(d + part * 8, valid ? src + part * 8 : src, valid);
+    }
+    return off;
+  };
+  auto load_tile = [&](int buf, long long mine) {
+    __nv_bfloat16* dst = Ks + (size_t)buf * BN * DP;
+#pragma unroll
+    for (int j = 0; j < KPW; ++j) {
+      const long long off = __shfl_sync(0xffffffffu, mine, j);
+      const bool valid = off >= 0;
+      const __nv_bfloat16* src = cache + (valid ? off : 0);
+      __nv_bfloat16* d = dst + (size_t)(warp + j * NW) * DP;
+      for (int part = lane; part < chunks; part += 32) cp_async16(d + part * 8, src + (valid ? part * 8 : 0), valid);
     }
   };
   auto group_barrier = [&]() {
@@ -172,6 +184,14 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
   // this thread's softmax row: the row group's 32 CH threads, TPR per row
   const int tg = ch * 32 + lane;
   const int srow = 16 * rg + tg / TPR, spart = tg % TPR;
+  // this lane's ldmatrix addresses (shared space, bytes): its row of the query fragments, of a key tile's score
+  // fragments, of the weight fragments, and of the value fragments (transposed loads)
+  const uint32_t qa_s = smem_addr(Qs + (size_t)(16 * rg + 8 * (mat & 1) + r8) * DP + 8 * (mat >> 1));
+  const uint32_t kb_s = KW == 16 ? smem_addr(Ks + (size_t)(KW * ch + 8 * (mat >> 1) + r8) * DP + 8 * (mat & 1))
+                                 : smem_addr(Ks + (size_t)(KW * ch + r8) * DP + 8 * (mat & 1));
+  const uint32_t ph_s = smem_addr(Ph + (size_t)(16 * rg + 8 * (mat & 1) + r8) * PP + 8 * (mat >> 1));
+  const uint32_t pl_s = smem_addr(Pl + (size_t)(16 * rg + 8 * (mat & 1) + r8) * PP + 8 * (mat >> 1));
+  const uint32_t vt_s = smem_addr(Ks + (size_t)(8 * (mat & 1) + r8) * DP + col0 + 8 * (mat >> 1));
   // the last key each of this thread's two score rows may see (-1: the row is past the portion)
   int row_pos[2];
 #pragma unroll
@@ -180,47 +200,57 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
     row_pos[half] = row < rows_total ? pos0 + (int)(row / H) : -1;
   }
 
-  if (t_begin < t_end) load_tile(t_begin, 0);
+  long long ahead = lookup(t_begin);
+  if (t_begin < t_end) load_tile(0, ahead);
   cp_async_commit();
+  ahead = lookup(t_begin + 1);
   for (int tile = t_begin; tile < t_end; ++tile) {
     const int buf = (tile - t_begin) & 1;
     cp_async_wait<0>();
     __syncthreads();                              // the tile is here, and everybody is done with the tile before
-    if (tile + 1 < t_end) load_tile(tile + 1, buf ^ 1);
+    if (tile + 1 < t_end) load_tile(buf ^ 1, ahead);
     cp_async_commit();
-    const __nv_bfloat16* Kt = Ks + (size_t)buf * BN * DP;
+    ahead = lookup(tile + 2);
     // ---- S: this warp's 16 rows x KW keys, two accumulator sets over alternating k steps
     {
       constexpr int NS = KW / 8;
-      float s[2][NS][4];
+      float s[4][NS][4];
 #pragma unroll
-      for (int x = 0; x < 2; ++x)
+      for (int x = 0; x < 4; ++x)
 #pragma unroll
         for (int y = 0; y < NS; ++y) s[x][y][0] = s[x][y][1] = s[x][y][2] = s[x][y][3] = 0.f;
-      const __nv_bfloat16* qa = Qs + (size_t)(16 * rg + 8 * (mat & 1) + r8) * DP + 8 * (mat >> 1);
-      const __nv_bfloat16* kb = KW == 16 ? Kt + (size_t)(KW * ch + 8 * (mat >> 1) + r8) * DP + 8 * (mat & 1)
-                                         : Kt + (size_t)(KW * ch + r8) * DP + 8 * (mat & 1);
+      const uint32_t kb = kb_s + (uint32_t)buf * (uint32_t)(BN * DP * 2);
       const int nks = D / 16;
-      auto step = [&](float (&acc)[NS][4], int ks) {
+      auto step = [&](float (&acc)[NS][4], uint32_t off) {       // off: bytes along the row, 32 per k step
         uint32_t a[4];
-        ldsm_x4(a, qa + 16 * ks);
+        ldsm_x4(a, qa_s + off);
         if (KW == 16) {
           uint32_t b[4];
-          ldsm_x4(b, kb + 16 * ks);
+          ldsm_x4(b, kb + off);
           mma_bf16(acc[0], a, b[0], b[1]);
           mma_bf16(acc[NS - 1], a, b[2], b[3]);
         } else {
           uint32_t b[2];
-          ldsm_x2(b, kb + 16 * ks);
+          ldsm_x2(b, kb + off);
           mma_bf16(acc[0], a, b[0], b[1]);
         }
       };
       int ks = 0;
-      for (; ks + 1 < nks; ks += 2) {
-        step(s[0], ks);
-        step(s[1], ks + 1);
+      for (; ks + 3 < nks; ks += 4) {              // four independent chains
+        const uint32_t off = 32u * ks;
+        step(s[0], off);
+        step(s[1], off + 32);
+        step(s[2], off + 64);
+        step(s[3], off + 96);
       }
-      if (ks < nks) step(s[0], ks);
+      for (; ks < nks; ++ks) step(s[0], 32u * ks);
+#pragma unroll
+      for (int y = 0; y < NS; ++y)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          s[0][y][x] += s[1][y][x];
+          s[2][y][x] += s[3][y][x];
+        }
 #pragma unroll
       for (int nt = 0; nt < NS; ++nt)
 #pragma unroll
@@ -229,8 +259,8 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
           const int c = KW * ch + 8 * nt + qcol;
           const int key = tile * BN + c;
           float2 v;
-          v.x = key <= row_pos[half] ? (s[0][nt][2 * half] + s[1][nt][2 * half]) * scale : -INFINITY;
-          v.y = key + 1 <= row_pos[half] ? (s[0][nt][2 * half + 1] + s[1][nt][2 * half + 1]) * scale : -INFINITY;
+          v.x = key <= row_pos[half] ? (s[0][nt][2 * half] + s[2][nt][2 * half]) * scale : -INFINITY;
+          v.y = key + 1 <= row_pos[half] ? (s[0][nt][2 * half + 1] + s[2][nt][2 * half + 1]) * scale : -INFINITY;
           *reinterpret_cast<float2*>(Ss + r * SP + c) = v;
         }
     }
@@ -285,22 +315,22 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
           o[i][0] *= c_lo; o[i][1] *= c_lo; o[i][2] *= c_hi; o[i][3] *= c_hi;
         }
       }
+      const uint32_t vt = vt_s + (uint32_t)buf * (uint32_t)(BN * DP * 2);
 #pragma unroll
       for (int kk = 0; kk < BN / 16; ++kk) {
         uint32_t ah[4], al[4];
-        ldsm_x4(ah, Ph + (size_t)(16 * rg + 8 * (mat & 1) + r8) * PP + 16 * kk + 8 * (mat >> 1));
-        ldsm_x4(al, Pl + (size_t)(16 * rg + 8 * (mat & 1) + r8) * PP + 16 * kk + 8 * (mat >> 1));
+        ldsm_x4(ah, ph_s + 32 * kk);
+        ldsm_x4(al, pl_s + 32 * kk);
+        const uint32_t vk = vt + (uint32_t)kk * (uint32_t)(16 * DP * 2);
 #pragma unroll
         for (int nd = 0; nd < NT; nd += 2) {
           if (nd < ntw) {
             uint32_t b[4];
-            ldsm_x4_trans(b, Kt + (size_t)(16 * kk + 8 * (mat & 1) + r8) * DP + col0 + 8 * (nd + (mat >> 1)));
+            ldsm_x4_trans(b, vk + 16 * nd);
             mma_bf16(o[nd], ah, b[0], b[1]);
+            if (nd + 1 < ntw) mma_bf16(o[nd + 1], ah, b[2], b[3]);
             mma_bf16(o[nd], al, b[0], b[1]);
-            if (nd + 1 < ntw) {
-              mma_bf16(o[nd + 1], ah, b[2], b[3]);
-              mma_bf16(o[nd + 1], al, b[2], b[3]);
-            }
+            if (nd + 1 < ntw) mma_bf16(o[nd + 1], al, b[2], b[3]);
           }
         }
       }
@@ -344,27 +374,41 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
   }
 }
 
-// out[row, :] = sum_s w_s O_s / sum_s w_s l_s with w_s = exp(m_s - max m), s ascending.  One block per (token, head).
+// out[row, :] = sum_s w_s O_s / sum_s w_s l_s with w_s = exp(m_s - max m), s ascending.  One block per (token, head):
+// the shares' weights are formed once (in parallel, into shared memory), then every thread adds its columns.
 __global__ void latent_attn_join_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
                                         __nv_bfloat16* __restrict__ out, long long o_row, long long o_head, int H,
                                         int R, int n_splits) {
   bspec::pdl_prologue(44);
+  __shared__ float w[64];
+  __shared__ float inv_l;
   const size_t row = blockIdx.x;
   const long long t = row / H;
   const int h = (int)(row % H);
-  float M = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml_part[2 * (row * n_splits + s)]);
-  float L = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float m = ml_part[2 * (row * n_splits + s)];
-    if (m != -INFINITY) L += expf(m - M) * ml_part[2 * (row * n_splits + s) + 1];
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float m0 = lane < n_splits ? ml_part[2 * (row * n_splits + lane)] : -INFINITY;
+    float m1 = lane + 32 < n_splits ? ml_part[2 * (row * n_splits + lane + 32)] : -INFINITY;
+    const float M = warp_max(fmaxf(m0, m1));
+    const float w0 = m0 == -INFINITY ? 0.f : expf(m0 - M), w1 = m1 == -INFINITY ? 0.f : expf(m1 - M);
+    w[lane] = w0;
+    w[lane + 32] = w1;
+    __syncwarp();
+    if (lane == 0) {                 // the sum in the order of the shares
+      float L = 0.f;
+      for (int s = 0; s < n_splits; ++s)
+        if (w[s] != 0.f) L += w[s] * ml_part[2 * (row * n_splits + s) + 1];
+      inv_l = 1.f / L;
+    }
   }
-  const float inv = 1.f / L;
+  __syncthreads();
+  const float inv = inv_l;
   for (int c = threadIdx.x; c < R; c += blockDim.x) {
     float acc = 0.f;
+#pragma unroll 4
     for (int s = 0; s < n_splits; ++s) {
-      const float m = ml_part[2 * (row * n_splits + s)];
-      if (m != -INFINITY) acc += expf(m - M) * o_part[(row * n_splits + s) * R + c];
+      const float x = o_part[(row * n_splits + s) * R + c];
+      if (w[s] != 0.f) acc += w[s] * x;
     }
     out[t * o_row + h * o_head + c] = __float2bfloat16_rn(acc * inv);
   }
@@ -400,7 +444,7 @@ BSPEC_API int bspec_latent_attention_mma(const void* ql, long long ql_row, long 
     return (int)cudaErrorInvalidValue;
   const int BM = bspec_latent_attention_mma_rows(max_q_len, H, R);
   const long long row_tiles = ((long long)max_q_len * H + BM - 1) / BM;
-  if (row_tiles > 2147483647ll || n_entries > 65535 || n_splits > 65535) return (int)cudaErrorInvalidConfiguration;
+  if ((long long)max_q_len * H > 2147483647ll || n_entries > 65535 || n_splits > 64) return (int)cudaErrorInvalidConfiguration;
   dim3 grid((unsigned)row_tiles, n_entries, n_splits);
   const size_t smem = smem_bytes(R + P, BM);
 #define LM(RG, CH, N)                                                                                                \

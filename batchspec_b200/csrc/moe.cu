@@ -26,24 +26,32 @@ template <typename T>
 __global__ void __launch_bounds__(ROUTE_THREADS)
 moe_route_kernel(const T* __restrict__ h, int d, const T* __restrict__ wr, const void* __restrict__ corr,
                  int corr_dtype, int E, int G, int keep, int top, float scale, int* __restrict__ ids,
-                 float* __restrict__ wts) {
+                 float* __restrict__ wts, const float* __restrict__ logits) {
   bspec::pdl_prologue(50);
   extern __shared__ float sm[];
   float* hs = sm;                 // [d]
   float* sc = hs + d;             // [E] sigmoid scores
   float* ch = sc + E;             // [E] choice scores (masked in place)
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) hs[i] = to_f32(h[(size_t)t * d + i]);
-  __syncthreads();
-  for (int e = warp; e < E; e += ROUTE_THREADS / 32) {
-    const T* w = wr + (size_t)e * d;
-    float z = 0.f;
-    for (int i = lane; i < d; i += 32) z += hs[i] * to_f32(w[i]);
-    z = warp_sum(z);
-    if (lane == 0) {
-      const float s = 1.f / (1.f + expf(-z));
+  if (logits != nullptr) {            // the logits were formed by a matrix product (many tokens)
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      const float s = 1.f / (1.f + expf(-logits[(size_t)t * E + e]));
       sc[e] = s;
       ch[e] = s + (corr != nullptr ? load_as_f32(corr, corr_dtype, e) : 0.f);
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) hs[i] = to_f32(h[(size_t)t * d + i]);
+    __syncthreads();
+    for (int e = warp; e < E; e += ROUTE_THREADS / 32) {
+      const T* w = wr + (size_t)e * d;
+      float z = 0.f;
+      for (int i = lane; i < d; i += 32) z += hs[i] * to_f32(w[i]);
+      z = warp_sum(z);
+      if (lane == 0) {
+        const float s = 1.f / (1.f + expf(-z));
+        sc[e] = s;
+        ch[e] = s + (corr != nullptr ? load_as_f32(corr, corr_dtype, e) : 0.f);
+      }
     }
   }
   __syncthreads();
@@ -280,6 +288,93 @@ moe_skinny_kernel(const __nv_bfloat16* __restrict__ A, const int* __restrict__ p
   }
 }
 
+// The same on the tensor cores (mma.sync m16n8k16, float32 accumulation) for K a multiple of 32: the WEIGHT rows
+// take the 16 rows of the product and the tile's (at most 16) token rows its 8 columns, twice.  A lane fetches 16
+// contiguous bytes of two weight rows straight from global memory (no staging: every weight is used once) and 16
+// bytes of a token row from shared memory; both sides number the 32 k of a step in the same permuted order
+// (lane l % 4 holds k = 8 (l % 4) .. + 7), which a sum over k does not notice.  Eight loads are in flight per lane.
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <typename TO, bool GELU, int RT>          // RT: token rows a tile may hold, 8 or 16
+__global__ void __launch_bounds__(256)
+moe_skinny_mma_kernel(const __nv_bfloat16* __restrict__ A, const int* __restrict__ perm, int top,
+                      const __nv_bfloat16* __restrict__ W, TO* __restrict__ C, int N, int K,
+                      const int* __restrict__ tiles, const int* __restrict__ n_tiles) {
+  bspec::pdl_prologue(56);
+  if ((int)blockIdx.y >= *n_tiles) return;
+  extern __shared__ uint4 Xs[];                   // [RT][K / 8 + 1]: token rows (rows past the tile are zero)
+  const int e = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int K8 = K / 8, XS = K8 + 1;              // the odd stride spreads the rows over the banks
+  for (int idx = tid; idx < RT * K8; idx += 256) {
+    const int r = idx / K8, c = idx - r * K8;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < rows) {
+      const int src = perm != nullptr ? perm[row0 + r] / top : row0 + r;
+      v = reinterpret_cast<const uint4*>(A + (size_t)src * K)[c];
+    }
+    Xs[r * XS + c] = v;
+  }
+  __syncthreads();
+  const int n0 = blockIdx.x * 128 + warp * 16;    // this warp's 16 weight rows
+  if (n0 >= N) return;
+  const int g = lane >> 2, q = lane & 3;
+  const __nv_bfloat16* We = W + (size_t)e * N * K;
+  const uint4* w_lo = reinterpret_cast<const uint4*>(We + (size_t)min(n0 + g, N - 1) * K) + q;
+  const uint4* w_hi = reinterpret_cast<const uint4*>(We + (size_t)min(n0 + g + 8, N - 1) * K) + q;
+  const uint4* x_lo = Xs + g * XS + q;            // token row g, and g + 8 for the second half
+  const uint4* x_hi = Xs + (RT == 16 ? g + 8 : g) * XS + q;
+  const bool two = RT == 16 && rows > 8;
+  float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+  const int steps = K / 32;
+  int s = 0;
+  for (; s + 3 < steps; s += 4) {
+    uint4 a[4], b[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      a[u] = __ldg(w_lo + 4 * (s + u));
+      b[u] = __ldg(w_hi + 4 * (s + u));
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint4 x = x_lo[4 * (s + u)];
+      mma_bf16_16816(acc0, a[u].x, b[u].x, a[u].y, b[u].y, x.x, x.y);
+      mma_bf16_16816(acc0, a[u].z, b[u].z, a[u].w, b[u].w, x.z, x.w);
+      if (two) {
+        const uint4 y = x_hi[4 * (s + u)];
+        mma_bf16_16816(acc1, a[u].x, b[u].x, a[u].y, b[u].y, y.x, y.y);
+        mma_bf16_16816(acc1, a[u].z, b[u].z, a[u].w, b[u].w, y.z, y.w);
+      }
+    }
+  }
+  for (; s < steps; ++s) {
+    const uint4 a = __ldg(w_lo + 4 * s), b = __ldg(w_hi + 4 * s), x = x_lo[4 * s];
+    mma_bf16_16816(acc0, a.x, b.x, a.y, b.y, x.x, x.y);
+    mma_bf16_16816(acc0, a.z, b.z, a.w, b.w, x.z, x.w);
+    if (two) {
+      const uint4 y = x_hi[4 * s];
+      mma_bf16_16816(acc1, a.x, b.x, a.y, b.y, y.x, y.y);
+      mma_bf16_16816(acc1, a.z, b.z, a.w, b.w, y.z, y.w);
+    }
+  }
+  // acc[0], acc[1]: weight row n0 + g, tokens 2 q and 2 q + 1;  acc[2], acc[3]: weight row n0 + g + 8
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const float* acc = half == 0 ? acc0 : acc1;
+    if (half == 1 && !two) break;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int tok = 8 * half + 2 * q + (i & 1), n = n0 + g + 8 * (i >> 1);
+      if (tok < rows && n < N) C[(size_t)(row0 + tok) * N + n] = from_f32<TO>(GELU ? gelu_erf(acc[i]) : acc[i]);
+    }
+  }
+}
+
 // sorted[r, :] = h[perm[r] / top, :]
 template <typename T>
 __global__ void moe_gather_kernel(const T* __restrict__ h, const int* __restrict__ perm, int top, T* __restrict__ out,
@@ -305,21 +400,21 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restri
 
 BSPEC_API int bspec_moe_route(const void* h, int dtype, int n, int d, const void* wr, const void* corr, int corr_dtype,
                               int E, int G, int keep, int top, float scale, int* ids, float* wts,
-                              cudaStream_t stream) {
+                              const float* logits, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (E <= 0 || E > MAX_EXPERTS || top <= 0 || top > E || G <= 0 || E % G || keep <= 0 || keep > G ||
       (long long)keep * (E / G) < top)
     return (int)cudaErrorInvalidValue;
-  const size_t smem = (size_t)(d + 2 * E + 8) * sizeof(float);
+  const size_t smem = (size_t)((d > 1024 ? d : 1024) + 2 * E + 8) * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   if (dtype == BSPEC_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     BSPEC_LAUNCH((moe_route_kernel<float>), n, ROUTE_THREADS, smem, stream, (const float*)h, d, (const float*)wr, corr,
-                 corr_dtype, E, G, keep, top, scale, ids, wts);
+                 corr_dtype, E, G, keep, top, scale, ids, wts, logits);
   } else {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     BSPEC_LAUNCH((moe_route_kernel<__nv_bfloat16>), n, ROUTE_THREADS, smem, stream, (const __nv_bfloat16*)h, d,
-                 (const __nv_bfloat16*)wr, corr, corr_dtype, E, G, keep, top, scale, ids, wts);
+                 (const __nv_bfloat16*)wr, corr, corr_dtype, E, G, keep, top, scale, ids, wts, logits);
   }
   return BSPEC_LAUNCH_CHECK();
 }
@@ -369,6 +464,32 @@ BSPEC_API int bspec_moe_skinny(const void* A, const int* perm, int top, const vo
   } while (0)
   if (out_dtype == BSPEC_F32) { if (gelu) LS(float, true); else LS(float, false); }
   else { if (gelu) LS(__nv_bfloat16, true); else LS(__nv_bfloat16, false); }
+#undef LS
+  return BSPEC_LAUNCH_CHECK();
+}
+
+// Tiles of at most `rows_per_tile` rows (8 or 16: a plan made with that BM), bfloat16 operands, K a multiple of 32.
+BSPEC_API int bspec_moe_skinny_mma(const void* A, const int* perm, int top, const void* W, void* C, int out_dtype,
+                                   int N, int K, const int* tiles, const int* n_tiles, int max_tiles, int gelu,
+                                   int rows_per_tile, cudaStream_t stream) {
+  if (max_tiles <= 0 || N <= 0) return 0;
+  if (K % 32 != 0 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
+    return (int)cudaErrorInvalidValue;
+  dim3 grid((N + 127) / 128, max_tiles);
+  if (grid.y > 65535) return (int)cudaErrorInvalidConfiguration;
+  if (rows_per_tile != 8 && rows_per_tile != 16) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)rows_per_tile * (K / 8 + 1) * 16;
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+#define LS(TO, G, RT)                                                                                               \
+  do {                                                                                                              \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_skinny_mma_kernel<TO, G, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    BSPEC_LAUNCH((moe_skinny_mma_kernel<TO, G, RT>), grid, 256, smem, stream, (const __nv_bfloat16*)A, perm, top,   \
+                 (const __nv_bfloat16*)W, (TO*)C, N, K, tiles, n_tiles);                                            \
+  } while (0)
+#define LR(TO, G) do { if (rows_per_tile == 16) LS(TO, G, 16); else LS(TO, G, 8); } while (0)
+  if (out_dtype == BSPEC_F32) { if (gelu) LR(float, true); else LR(float, false); }
+  else { if (gelu) LR(__nv_bfloat16, true); else LR(__nv_bfloat16, false); }
+#undef LR
 #undef LS
   return BSPEC_LAUNCH_CHECK();
 }

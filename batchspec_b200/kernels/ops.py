@@ -66,12 +66,14 @@ _SIGNATURES = {
                                    c_void_p, c_float, c_void_p],
     "bspec_gate_heads": [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "bspec_moe_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                        c_void_p, c_void_p, c_void_p],
+                        c_void_p, c_void_p, c_void_p, c_void_p],
     "bspec_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "bspec_moe_grouped": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                           c_int, c_int, c_int, c_void_p],
     "bspec_moe_skinny": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                          c_int, c_void_p],
+    "bspec_moe_skinny_mma": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                             c_int, c_int, c_void_p],
     "bspec_moe_gather": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
     "bspec_moe_combine": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
     "bspec_sgemm_tn_batched": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
@@ -140,7 +142,7 @@ TRACE_KERNEL_NAMES = {1: "embed", 2: "add_rmsnorm", 3: "gather_rows_add", 4: "si
                       11: "sample_threshold", 12: "sample_pick", 13: "sample_final", 14: "add_layernorm", 15: "clamped_glu",
                       16: "gelu_erf", 17: "tanh_softcap", 20: "gemm_tcgen05", 30: "attn_prefill_tc", 40: "latent_prepare",
                       41: "latent_attn_generic", 42: "gate_heads", 43: "latent_attn_mma", 44: "latent_attn_join",
-                      50: "moe_route", 51: "moe_plan", 52: "moe_grouped", 53: "moe_gather", 54: "moe_combine", 55: "moe_skinny"}
+                      50: "moe_route", 51: "moe_plan", 52: "moe_grouped", 53: "moe_gather", 54: "moe_combine", 55: "moe_skinny", 56: "moe_skinny_mma"}
 
 
 def set_trace(buf: Optional[torch.Tensor], count: Optional[torch.Tensor]) -> None:
@@ -753,10 +755,10 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor
         row_tiles = -(-(ctx.max_q_len * n_heads) // rows)
         n_splits = 1
         if ctx.max_q_len * n_heads <= 256:
-            # as many shares as fill the CTAs that are resident at once (one wave), at least 128 keys each
+            # as many shares as fill the CTAs that are resident at once (one wave), at least 256 keys each
             smem = (rows + 64) * (kv_rank + rot_dim + 8) * 2 + rows * 330
             slots = sm_count(q_lat.device) * max(1, min(4, (220 * 1024) // smem))
-            n_splits = max(1, min(64, slots // (ctx.n_entries * row_tiles), -(-ctx.max_kv_len // 128)))
+            n_splits = max(1, min(64, slots // (ctx.n_entries * row_tiles), -(-ctx.max_kv_len // 256)))
         o_part = ml_part = None
         if n_splits > 1:
             o_part = torch.empty((n * H * n_splits * R,), dtype=torch.float32, device=q_lat.device)
@@ -801,6 +803,8 @@ def gate_heads(v: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None:
 
 MOE_LIBRARY_GROUPED = True       # bfloat16 steps with many rows per expert: the vendor library's grouped product
 MOE_LIBRARY_MIN_ROWS = 32        # ... from this many (token, choice) rows per expert on average
+MOE_ROUTE_FUSED_MAX = 0          # up to this many tokens the router's logits are formed inside its kernel (else: a product)
+MOE_SKINNY_MMA = True            # ... its tensor-core form, for inner sizes that are multiples of 32
 MOE_SKINNY = True                # bfloat16 steps with fewer rows per expert: the weight-streaming kernel
 
 
@@ -813,10 +817,12 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.
     assert router.shape == (E, d) and router.dtype == h.dtype and h.is_contiguous() and router.is_contiguous()
     ids = torch.empty((n, top), dtype=torch.int32, device=h.device)
     wts = torch.empty((n, top), dtype=torch.float32, device=h.device)
+    # many tokens: the logits as one matrix product with float32 accumulation and output; few: inside the kernel
+    logits = linear(h, router, out_dtype=torch.float32) if n > MOE_ROUTE_FUSED_MAX else None
     _check(load_library().bspec_moe_route(h.data_ptr(), _dtype_code(h.dtype), n, d, router.data_ptr(), _ptr(correction),
                                           _dtype_code(correction.dtype) if correction is not None else F32, E,
                                           int(n_groups), int(keep), int(top), float(scale), ids.data_ptr(),
-                                          wts.data_ptr(), _stream()), "moe_route")
+                                          wts.data_ptr(), _ptr(logits), _stream()), "moe_route")
     return ids, wts
 
 
@@ -838,7 +844,11 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: tor
     # few rows per expert in bfloat16: tiles of 8 rows on the kernel that streams the experts' weights
     skinny = (not library and MOE_SKINNY and h.dtype == torch.bfloat16 and slots < 32 * E and d % 8 == 0
               and ff % 8 == 0 and 16 * max(d, ff) <= 200 * 1024)
-    BM = 8 if skinny else (64 if slots >= 32 * E else 16)
+    # ... on the tensor cores when both inner sizes are multiples of 32 and 16 token rows fit shared memory
+    skinny_mma = skinny and MOE_SKINNY_MMA and d % 32 == 0 and ff % 32 == 0
+    # 16 token rows per tile while they leave room for three CTAs per SM and there are that many rows per expert
+    mma_rows = 16 if (32 * max(d, ff) <= 72 * 1024 and slots > 4 * E) else 8
+    BM = (mma_rows if skinny_mma else 8) if skinny else (64 if slots >= 32 * E else 16)
     max_tiles = min(slots, slots // BM + E)
     meta = torch.empty((2 * slots + E + 1 + 3 * max_tiles + 1,), dtype=torch.int32, device=dev)
     perm, inv = meta[:slots], meta[slots:2 * slots]
@@ -855,6 +865,13 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: tor
         u = torch._grouped_mm(rows, w_up.transpose(1, 2), offs=ends)
         gelu_erf_(u)
         y = torch._grouped_mm(u, w_down.transpose(1, 2), offs=ends)
+    elif skinny_mma:
+        u = torch.empty((slots, ff), dtype=h.dtype, device=dev)
+        y = torch.empty((slots, d), dtype=torch.float32, device=dev)
+        _check(lib.bspec_moe_skinny_mma(h.data_ptr(), perm.data_ptr(), top, w_up.data_ptr(), u.data_ptr(), code, ff, d,
+                                        tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, 1, mma_rows, _stream()), "moe_skinny_mma_up")
+        _check(lib.bspec_moe_skinny_mma(u.data_ptr(), None, top, w_down.data_ptr(), y.data_ptr(), F32, d, ff,
+                                        tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, 0, mma_rows, _stream()), "moe_skinny_mma_down")
     elif skinny:
         u = torch.empty((slots, ff), dtype=h.dtype, device=dev)
         y = torch.empty((slots, d), dtype=torch.float32, device=dev)

@@ -337,8 +337,18 @@ def test_router_groups_and_negative_choices(ops, dtype, E, G, keep, top):
     h = torch.randn(n, d, device=DEV, generator=g).to(dtype)
     wr = (0.3 * torch.randn(E, d, device=DEV, generator=g)).to(dtype)
     corr = (-3.0 + 0.3 * torch.randn(E, device=DEV, generator=g)).to(dtype)
-    ids, wts = ops.moe_route(h, wr, corr, G, keep, top, 1.7)
     w = {"router": wr.double().cpu(), "correction": corr.double().cpu()}
+    for fused_max in (0, 1 << 30):                 # logits by a matrix product; logits inside the kernel
+        was = ops.MOE_ROUTE_FUSED_MAX
+        ops.MOE_ROUTE_FUSED_MAX = fused_max
+        try:
+            ids, wts = ops.moe_route(h, wr, corr, G, keep, top, 1.7)
+        finally:
+            ops.MOE_ROUTE_FUSED_MAX = was
+        _check_routing(h, w, ids, wts, E, G, keep, top, n, dtype)
+
+
+def _check_routing(h, w, ids, wts, E, G, keep, top, n, dtype):
     want_ids, want_w = P.route(h.double().cpu(), w, "", dict(experts=E, top=top, scale=1.7, groups=dict(count=G, keep=keep)))
     s = torch.sigmoid(h.double().cpu() @ w["router"].T)
     assert ((s + w["correction"]) < 0).all()
@@ -355,7 +365,8 @@ def test_router_groups_and_negative_choices(ops, dtype, E, G, keep, top):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n,E,top,d,ff", [(1, 4, 2, 32, 24), (9, 6, 3, 100, 36), (300, 8, 4, 64, 40), (40, 16, 1, 72, 8),
-                                          (8, 64, 6, 512, 136), (64, 32, 4, 264, 1032)])
+                                          (8, 64, 6, 512, 136), (64, 32, 4, 264, 1032), (8, 64, 6, 512, 160),
+                                          (64, 16, 4, 288, 1056), (3, 8, 2, 2048, 96)])
 def test_routed_experts(ops, dtype, n, E, top, d, ff):
     g = torch.Generator(device=DEV).manual_seed(n)
     h = torch.randn(n, d, device=DEV, generator=g).to(dtype)
@@ -365,13 +376,14 @@ def test_routed_experts(ops, dtype, n, E, top, d, ff):
     if n > 8:
         ids[3:8] = ids[3]                          # some experts with many rows, some perhaps with none
     wts = torch.rand(n, top, device=DEV, generator=g) + 0.1
-    for library, skinny in ((False, True), (False, False), (True, True)):     # the three kinds of grouped product
-        was = ops.MOE_LIBRARY_MIN_ROWS, ops.MOE_SKINNY
-        ops.MOE_LIBRARY_MIN_ROWS, ops.MOE_SKINNY = (0 if library else 1 << 30), skinny
+    # the kinds of grouped product: weight-streaming on the tensor cores, the same with plain arithmetic, tiled, library
+    for library, skinny, mma in ((False, True, True), (False, True, False), (False, False, False), (True, True, True)):
+        was = ops.MOE_LIBRARY_MIN_ROWS, ops.MOE_SKINNY, ops.MOE_SKINNY_MMA
+        ops.MOE_LIBRARY_MIN_ROWS, ops.MOE_SKINNY, ops.MOE_SKINNY_MMA = (0 if library else 1 << 30), skinny, mma
         try:
             out = ops.moe_experts(h, ids, wts, w_up, w_down, dtype)
         finally:
-            ops.MOE_LIBRARY_MIN_ROWS, ops.MOE_SKINNY = was
+            ops.MOE_LIBRARY_MIN_ROWS, ops.MOE_SKINNY, ops.MOE_SKINNY_MMA = was
         want = torch.zeros(n, d, dtype=torch.float64)
         for t in range(n):
             for k in range(top):
