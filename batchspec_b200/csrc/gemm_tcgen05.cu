@@ -45,7 +45,9 @@ struct GemmParams {
   int splits;
   int kblocks_per_split;
   int stages;
-  int glu;               // rows of W come in groups of 16 = 8 gate rows + their 8 up rows; C[M, N/2] = silu(gate) * up
+  int glu;               // rows of W come in groups of 16 = 8 gate rows + their 8 up rows; C[M, N/2] = act(gate, up):
+                         // 1: silu(gate) * up;  2: g sigmoid(alpha g) (u + 1), g = min(gate, limit), u = clamp(up, +-limit)
+  float glu_alpha, glu_limit;
   int prefetch_kb;       // K blocks of weights (beyond the stages) to pull into the L2 before waiting on the predecessor
   // fused q/k/v projection (rope_freq != nullptr): tile t of W is head t (q heads, then k heads, then v heads)
   const float* rope_freq;    // [2][64] frequencies as two floats each (see elementwise.cu, rope_sincos)
@@ -69,6 +71,16 @@ __device__ __forceinline__ void rope_sincos64(int pos, const float* __restrict__
 __device__ __forceinline__ void store_out(void* C, int out_f32, size_t idx, float v) {
   if (out_f32) reinterpret_cast<float*>(C)[idx] = v;
   else reinterpret_cast<__nv_bfloat16*>(C)[idx] = __float2bfloat16_rn(v);
+}
+
+// What the gated epilogues make of a gate and an up value (GemmParams::glu).
+__device__ __forceinline__ float glu_combine(int kind, float alpha, float limit, float g, float u) {
+  if (kind == 2) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+  }
+  return g / (1.f + expf(-g)) * u;
 }
 
 __global__ void __launch_bounds__(GEMM_THREADS)
@@ -200,7 +212,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               if (n0 + 8 + j < p.N) {
                 const float gte = __uint_as_float(v[j]);
                 store_out(p.C, p.out_f32, (size_t)ra * (p.N / 2) + (n0 >> 1) + j,
-                          gte / (1.f + expf(-gte)) * __uint_as_float(v[8 + j]));
+                          glu_combine(p.glu, p.glu_alpha, p.glu_limit, gte, __uint_as_float(v[8 + j])));
               }
           }
         } else if (!p.swap) {
@@ -292,7 +304,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                   acc += v[t][s];
                   if (p.glu) acc_u += u[t][s];
                 }
-              if (p.glu) acc = acc / (1.f + expf(-acc)) * acc_u;
+              if (p.glu) acc = glu_combine(p.glu, p.glu_alpha, p.glu_limit, acc, acc_u);
             }
             res[t] = acc;
           }
@@ -424,13 +436,15 @@ struct RopeEpilogue {
 };
 
 static int launch_gemm(const void* X, const void* W, void* C, int M, int N, int K, int out_f32, int glu, int* status,
-                       int sm_count, const RopeEpilogue* rope, cudaStream_t stream) {
+                       int sm_count, const RopeEpilogue* rope, cudaStream_t stream, float glu_alpha = 1.f,
+                       float glu_limit = 0.f) {
   int plan[5];
   if (bspec_gemm_tc_plan(M, N, K, sm_count, plan) < 0) return (int)cudaErrorInvalidValue;
   if (glu && (N % 16 != 0)) return (int)cudaErrorInvalidValue;
   GemmParams p;
   p.C = C; p.status = status;
-  p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.glu = glu ? 1 : 0;
+  p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.glu = glu == 2 ? 2 : (glu ? 1 : 0);
+  p.glu_alpha = glu_alpha; p.glu_limit = glu_limit;
   p.swap = plan[0]; p.bn = plan[1]; p.splits = plan[2]; p.stages = plan[3];
   p.rope_freq = nullptr; p.positions = p.tok_entry = p.kv_indptr = p.kv_indices = nullptr; p.cache = nullptr;
   p.Hq = p.Hkv = p.page_size = p.interleaved = p.write_kv = 0;
@@ -498,6 +512,13 @@ static int launch_gemm(const void* X, const void* W, void* C, int M, int N, int 
 BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N, int K, int out_f32, int glu,
                             int* status, int sm_count, cudaStream_t stream) {
   return launch_gemm(X, W, C, M, N, K, out_f32, glu, status, sm_count, nullptr, stream);
+}
+
+// The same with the clamped gated activation in the epilogue: C[M, N/2] = g sigmoid(alpha g) (u + 1) with
+// g = min(gate, limit), u = clamp(up, -limit, limit); W's rows in groups of 8 gate rows and their 8 up rows.
+BSPEC_API int bspec_gemm_tc_clamped_glu(const void* X, const void* W, void* C, int M, int N, int K, float alpha,
+                                        float limit, int* status, int sm_count, cudaStream_t stream) {
+  return launch_gemm(X, W, C, M, N, K, 0, 2, status, sm_count, nullptr, stream, alpha, limit);
 }
 
 // The fused q/k/v projection of an attention layer with head size 128 for a step of at most 128 tokens:

@@ -85,6 +85,8 @@ _SIGNATURES = {
                              c_int, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p],
     "bspec_gemm_tc_plan": [c_int, c_int, c_int, c_int, c_void_p],
     "bspec_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "bspec_gemm_tc_clamped_glu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p, c_int,
+                                  c_void_p],
     "bspec_gemm_tc_qkv_rope": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong,
                                c_void_p],
@@ -317,6 +319,25 @@ def linear_glu(x: torch.Tensor, w13: torch.Tensor, group: int = GLU_GROUP) -> to
     u = linear(x, w13)
     out = torch.empty((M, inter), dtype=x.dtype, device=x.device)
     silu_mul(u, out, group)
+    return out
+
+
+def linear_clamped_glu(x: torch.Tensor, w13: torch.Tensor, alpha: float, limit: float, group: int = GLU_GROUP) -> torch.Tensor:
+    """g sigmoid(alpha g) (u + 1) with g = min(x Wg^T, limit), u = clamp(x Wu^T, -limit, limit), for ``w13`` interleaved
+    by ``interleave_gate_up``: one kernel with the activation in the product's epilogue for decode-sized bfloat16
+    steps, else product + activation kernel."""
+    _require_cuda(x, w13)
+    M, K = x.shape
+    N = w13.shape[0]
+    inter = N // 2
+    out = torch.empty((M, inter), dtype=x.dtype, device=x.device)
+    if (GLU_FUSION and x.dtype == torch.bfloat16 and K % 8 == 0 and M > 0 and group == GLU_GROUP and N % 16 == 0
+            and x.is_contiguous() and (TC_GEMM == "all" or (TC_GEMM == "auto" and M <= TC_GEMM_MAX_M))):
+        _check(load_library().bspec_gemm_tc_clamped_glu(x.data_ptr(), w13.data_ptr(), out.data_ptr(), M, N, K,
+                                                        float(alpha), float(limit), _status_word(x.device).data_ptr(),
+                                                        sm_count(x.device), _stream()), "gemm_tc_clamped_glu")
+        return out
+    clamped_glu(linear(x, w13), out, alpha, limit, group)
     return out
 
 

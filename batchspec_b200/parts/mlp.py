@@ -67,14 +67,25 @@ class ClampedGLU(FeedForward):
                 "down": ParamSpec((self.dim, self.intermediate))}
 
     def bind(self, params):
-        self.w13 = torch.cat([params["gate"], params["up"]], dim=0).contiguous()
+        # bfloat16: gate and up rows interleaved in groups, so that the product's epilogue can apply the activation
+        # in decode-sized steps; float32: [gate; up] halves
+        self.group = ops.GLU_GROUP if (self.runtime.dtype == torch.bfloat16
+                                       and self.intermediate % ops.GLU_GROUP == 0) else 0
+        if self.group:
+            self.w13 = ops.interleave_gate_up(params["gate"], params["up"], self.group)
+        else:
+            self.w13 = torch.cat([params["gate"], params["up"]], dim=0).contiguous()
         self.w2 = params["down"].contiguous()
 
     def forward(self, x, ctx):
-        with bucket("mlp.gate_up_proj"):
-            u = ops.linear(x, self.w13)
-        m = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
-        with bucket("mlp.act"):
-            ops.clamped_glu(u, m, self.alpha, self.limit)
+        if self.group:
+            with bucket("mlp.gate_up_proj"):
+                m = ops.linear_clamped_glu(x, self.w13, self.alpha, self.limit, self.group)
+        else:
+            with bucket("mlp.gate_up_proj"):
+                u = ops.linear(x, self.w13)
+            m = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
+            with bucket("mlp.act"):
+                ops.clamped_glu(u, m, self.alpha, self.limit)
         with bucket("mlp.down_proj"):
             return ops.linear(m, self.w2)

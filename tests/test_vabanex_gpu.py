@@ -137,6 +137,28 @@ def test_clamped_glu_and_gelu_and_softcap(ops, dtype):
     assert (ops.tanh_softcap_(z.clone(), 12.5).double() - want).abs().max() <= 1e-5
 
 
+@pytest.mark.parametrize("M,I,K", [(1, 80, 64), (8, 8448, 2048), (5, 176, 72), (40, 256, 96), (3, 52, 64)])
+def test_clamped_glu_in_the_products_epilogue(ops, M, I, K):
+    """bfloat16 gate/up product with the clamped activation: decode-sized steps apply it in the product's epilogue
+    (weights interleaved in groups of 8), larger ones in a kernel of its own; both against float64."""
+    g = torch.Generator(device=DEV).manual_seed(M + I)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    wg = (2.0 * torch.randn(I, K, device=DEV, generator=g) / K ** 0.5).bfloat16()
+    wu = (2.0 * torch.randn(I, K, device=DEV, generator=g) / K ** 0.5).bfloat16()
+    L, alpha = 1.1, 1.702
+    gate = (x.double() @ wg.double().T).clamp(max=L)
+    up = (x.double() @ wu.double().T).clamp(-L, L)
+    want = gate * torch.sigmoid(alpha * gate) * (up + 1)
+    if I % ops.GLU_GROUP == 0:
+        got = ops.linear_clamped_glu(x, ops.interleave_gate_up(wg, wu), alpha, L)
+    else:
+        got = torch.empty(M, I, device=DEV, dtype=torch.bfloat16)
+        ops.clamped_glu(ops.linear(x, torch.cat([wg, wu])), got, alpha, L)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert (got.double() - want).abs().max() <= 3e-2 * max(1.0, want.abs().max().item())
+
+
 def test_yarn_frequencies_and_rotation_of_strided_heads(ops):
     from batchspec_b200.parts.rope import rope_inv_freq, yarn_magnitude
     for rot in (dict(base=250.0, dims=16, scaling=dict(factor=6.0, original=40, fast=10.0, slow=1.5)),
