@@ -387,11 +387,47 @@ __global__ void clamped_glu_kernel(const T* __restrict__ u, T* __restrict__ m, i
   }
 }
 
+// the same, eight bfloat16 per thread (I, and the group if any, multiples of 8): the launch shape of silu_mul's
+__global__ void clamped_glu_bf16x8_kernel(const __nv_bfloat16* __restrict__ u, __nv_bfloat16* __restrict__ m, int inter,
+                                          int n, int group, float alpha, float limit) {
+  bspec::pdl_prologue(15);
+  const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c8 * 8 >= inter) return;
+  const int col = c8 * 8;
+  const int gcol = group > 0 ? (col / group) * 2 * group + (col % group) : col;
+  const int ucol = group > 0 ? gcol + group : inter + col;
+  for (int row = blockIdx.y; row < n; row += gridDim.y) {
+    const __nv_bfloat16* src = u + (size_t)row * 2 * inter;
+    const uint4 gv = *reinterpret_cast<const uint4*>(src + gcol);
+    const uint4 uv = *reinterpret_cast<const uint4*>(src + ucol);
+    const __nv_bfloat16* g8 = reinterpret_cast<const __nv_bfloat16*>(&gv);
+    const __nv_bfloat16* u8 = reinterpret_cast<const __nv_bfloat16*>(&uv);
+    uint4 ov;
+    __nv_bfloat16* o8 = reinterpret_cast<__nv_bfloat16*>(&ov);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float g = fminf(__bfloat162float(g8[j]), limit);
+      const float up = fminf(fmaxf(__bfloat162float(u8[j]), -limit), limit);
+      o8[j] = __float2bfloat16_rn(g / (1.f + expf(-alpha * g)) * (up + 1.f));
+    }
+    *reinterpret_cast<uint4*>(m + (size_t)row * inter + col) = ov;
+  }
+}
+
 BSPEC_API int bspec_clamped_glu(const void* u, void* m, int dtype, int n, int inter, int group, float alpha,
                                 float limit, cudaStream_t stream) {
   const size_t total = (size_t)n * inter;
   if (total == 0) return 0;
   if (group < 0 || (group > 0 && inter % group != 0)) return (int)cudaErrorInvalidValue;
+  if (dtype == BSPEC_BF16 && inter % 8 == 0 && group % 8 == 0 && !(reinterpret_cast<uintptr_t>(u) & 15) &&
+      !(reinterpret_cast<uintptr_t>(m) & 15)) {
+    const int inter8 = inter / 8;
+    const int tx = inter8 >= 256 ? 256 : ((inter8 + 31) / 32) * 32;
+    const dim3 grid((inter8 + tx - 1) / tx, n > 32768 ? 32768 : n);
+    BSPEC_LAUNCH((clamped_glu_bf16x8_kernel), grid, tx, 0, stream, (const __nv_bfloat16*)u, (__nv_bfloat16*)m, inter, n,
+                 group, alpha, limit);
+    return BSPEC_LAUNCH_CHECK();
+  }
   const int threads = 256;
   size_t want = (total + threads - 1) / threads;
   const size_t cap = (size_t)bspec::sm_count() * 32;
@@ -414,8 +450,28 @@ __global__ void gelu_erf_kernel(T* __restrict__ x, size_t total) {
   }
 }
 
+__global__ void gelu_erf_bf16x8_kernel(uint4* __restrict__ x, size_t total8) {
+  bspec::pdl_prologue(16);
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
+    uint4 v = x[idx];
+    __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float f = __bfloat162float(e[j]);
+      e[j] = __float2bfloat16_rn(0.5f * f * (1.f + erff(f * 0.70710678118654752440f)));
+    }
+    x[idx] = v;
+  }
+}
+
 BSPEC_API int bspec_gelu_erf(void* x, int dtype, long long total, cudaStream_t stream) {
   if (total <= 0) return 0;
+  if (dtype == BSPEC_BF16 && total % 8 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15)) {
+    const size_t total8 = (size_t)total / 8;
+    const size_t want8 = (total8 + 255) / 256, cap8 = (size_t)bspec::sm_count() * 16;
+    BSPEC_LAUNCH((gelu_erf_bf16x8_kernel), (int)(want8 > cap8 ? cap8 : want8), 256, 0, stream, (uint4*)x, total8);
+    return BSPEC_LAUNCH_CHECK();
+  }
   const int threads = 256;
   size_t want = ((size_t)total + threads - 1) / threads;
   const size_t cap = (size_t)bspec::sm_count() * 32;

@@ -156,6 +156,55 @@ moe_plan_kernel(const int* __restrict__ ids, int slots, int E, int BM, int* __re
   }
 }
 
+// The same plan for many rows, in three kernels over all SMs.  Rows of one expert are placed in the order in which
+// their warps reach the expert's counter, so the placement (not any value: a row's result does not depend on where
+// it lies) may differ from run to run.
+__global__ void __launch_bounds__(256)
+moe_rank_kernel(const int* __restrict__ ids, int slots, int* __restrict__ counts, int* __restrict__ rank) {
+  bspec::pdl_prologue(57);
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = s < slots;
+  const int e = live ? ids[s] : -1;
+  const unsigned same = __match_any_sync(0xffffffffu, e);
+  const int lane = threadIdx.x & 31;
+  const int leader = __ffs(same) - 1;
+  int base = 0;
+  if (live && lane == leader) base = atomicAdd(&counts[e], __popc(same));
+  base = __shfl_sync(0xffffffffu, base, leader);
+  if (live) rank[s] = base + __popc(same & ((1u << lane) - 1u));
+}
+
+__global__ void moe_offsets_kernel(const int* __restrict__ counts, int E, int BM, int* __restrict__ offsets,
+                                   int* __restrict__ tiles, int* __restrict__ n_tiles_out, int max_tiles) {
+  bspec::pdl_prologue(58);
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int run = 0, nt = 0;
+  for (int e = 0; e < E; ++e) {
+    const int c = counts[e];
+    offsets[e] = run;
+    for (int r = 0; r < c && nt < max_tiles; r += BM) {
+      tiles[3 * nt] = e;
+      tiles[3 * nt + 1] = run + r;
+      tiles[3 * nt + 2] = min(BM, c - r);
+      ++nt;
+    }
+    run += c;
+  }
+  offsets[E] = run;
+  *n_tiles_out = nt;
+}
+
+__global__ void __launch_bounds__(256)
+moe_place_kernel(const int* __restrict__ ids, const int* __restrict__ rank, const int* __restrict__ offsets, int slots,
+                 int* __restrict__ perm, int* __restrict__ inv) {
+  bspec::pdl_prologue(59);
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= slots) return;
+  const int r = offsets[ids[s]] + rank[s];
+  perm[r] = s;
+  inv[s] = r;
+}
+
 __device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f)); }
 
 // A [*, K] rows; row r of the sorted order reads A[perm[r] / top] when perm is given (the up projection), else
@@ -375,13 +424,20 @@ moe_skinny_mma_kernel(const __nv_bfloat16* __restrict__ A, const int* __restrict
   }
 }
 
-// sorted[r, :] = h[perm[r] / top, :]
+// sorted[r, :] = h[perm[r] / top, :]   (16-byte pieces when the rows allow it)
 template <typename T>
 __global__ void moe_gather_kernel(const T* __restrict__ h, const int* __restrict__ perm, int top, T* __restrict__ out,
-                                  int d) {
+                                  int d, int vec) {
   bspec::pdl_prologue(53);
   const size_t src = (size_t)(perm[blockIdx.x] / top) * d, dst = (size_t)blockIdx.x * d;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) out[dst + i] = h[src + i];
+  if (vec) {
+    const int n16 = d * (int)sizeof(T) / 16;
+    const uint4* a = reinterpret_cast<const uint4*>(h + src);
+    uint4* b = reinterpret_cast<uint4*>(out + dst);
+    for (int i = threadIdx.x; i < n16; i += blockDim.x) b[i] = a[i];
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) out[dst + i] = h[src + i];
+  }
 }
 
 template <typename TY, typename TO>
@@ -389,10 +445,18 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restri
                                    int top, TO* __restrict__ out, int d) {
   bspec::pdl_prologue(54);
   const int t = blockIdx.x;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    float acc = 0.f;
-    for (int k = 0; k < top; ++k) acc += wts[(size_t)t * top + k] * to_f32(y[(size_t)inv[(size_t)t * top + k] * d + i]);
-    out[(size_t)t * d + i] = from_f32<TO>(acc);
+  for (int i = 2 * threadIdx.x; i < d; i += 2 * blockDim.x) {
+    float a0 = 0.f, a1 = 0.f;
+    const bool pair = i + 1 < d && (d % 2) == 0;
+    for (int k = 0; k < top; ++k) {
+      const float w = wts[(size_t)t * top + k];
+      const TY* row = y + (size_t)inv[(size_t)t * top + k] * d + i;
+      a0 += w * to_f32(row[0]);
+      if (i + 1 < d) a1 += w * to_f32(row[1]);
+    }
+    out[(size_t)t * d + i] = from_f32<TO>(a0);
+    if (i + 1 < d) out[(size_t)t * d + i + 1] = from_f32<TO>(a1);
+    (void)pair;
   }
 }
 
@@ -419,11 +483,21 @@ BSPEC_API int bspec_moe_route(const void* h, int dtype, int n, int d, const void
   return BSPEC_LAUNCH_CHECK();
 }
 
+// counts [E] and rank [slots]: scratch of the many-rows path (may be null: the one-block kernel then runs).
 BSPEC_API int bspec_moe_plan(const int* ids, int slots, int E, int BM, int* perm, int* inv, int* offsets, int* tiles,
-                             int* n_tiles, int max_tiles, cudaStream_t stream) {
+                             int* n_tiles, int max_tiles, int* counts, int* rank, cudaStream_t stream) {
   if (slots <= 0) return 0;
   if (E <= 0 || E > MAX_EXPERTS || (BM != 8 && BM != 16 && BM != 64)) return (int)cudaErrorInvalidValue;
-  BSPEC_LAUNCH((moe_plan_kernel), 1, 1024, 0, stream, ids, slots, E, BM, perm, inv, offsets, tiles, n_tiles, max_tiles);
+  if (slots <= 2048 || counts == nullptr || rank == nullptr) {
+    BSPEC_LAUNCH((moe_plan_kernel), 1, 1024, 0, stream, ids, slots, E, BM, perm, inv, offsets, tiles, n_tiles, max_tiles);
+    return BSPEC_LAUNCH_CHECK();
+  }
+  cudaError_t err = cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int), stream);
+  if (err != cudaSuccess) return (int)err;
+  const int blocks = (slots + 255) / 256;
+  BSPEC_LAUNCH((moe_rank_kernel), blocks, 256, 0, stream, ids, slots, counts, rank);
+  BSPEC_LAUNCH((moe_offsets_kernel), 1, 32, 0, stream, (const int*)counts, E, BM, offsets, tiles, n_tiles, max_tiles);
+  BSPEC_LAUNCH((moe_place_kernel), blocks, 256, 0, stream, ids, (const int*)rank, (const int*)offsets, slots, perm, inv);
   return BSPEC_LAUNCH_CHECK();
 }
 
@@ -498,10 +572,12 @@ BSPEC_API int bspec_moe_gather(const void* h, int dtype, const int* perm, int to
                                cudaStream_t stream) {
   if (slots <= 0) return 0;
   if (dtype == BSPEC_F32)
-    BSPEC_LAUNCH((moe_gather_kernel<float>), slots, 128, 0, stream, (const float*)h, perm, top, (float*)out, d);
+    BSPEC_LAUNCH((moe_gather_kernel<float>), slots, 128, 0, stream, (const float*)h, perm, top, (float*)out, d,
+                 (int)(d % 4 == 0 && !(reinterpret_cast<uintptr_t>(h) & 15) && !(reinterpret_cast<uintptr_t>(out) & 15)));
   else
     BSPEC_LAUNCH((moe_gather_kernel<__nv_bfloat16>), slots, 128, 0, stream, (const __nv_bfloat16*)h, perm, top,
-                 (__nv_bfloat16*)out, d);
+                 (__nv_bfloat16*)out, d,
+                 (int)(d % 8 == 0 && !(reinterpret_cast<uintptr_t>(h) & 15) && !(reinterpret_cast<uintptr_t>(out) & 15)));
   return BSPEC_LAUNCH_CHECK();
 }
 

@@ -67,7 +67,8 @@ _SIGNATURES = {
     "bspec_gate_heads": [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "bspec_moe_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                         c_void_p, c_void_p, c_void_p, c_void_p],
-    "bspec_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "bspec_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                       c_void_p, c_void_p],
     "bspec_moe_grouped": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                           c_int, c_int, c_int, c_void_p],
     "bspec_moe_skinny": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
@@ -144,7 +145,7 @@ TRACE_KERNEL_NAMES = {1: "embed", 2: "add_rmsnorm", 3: "gather_rows_add", 4: "si
                       11: "sample_threshold", 12: "sample_pick", 13: "sample_final", 14: "add_layernorm", 15: "clamped_glu",
                       16: "gelu_erf", 17: "tanh_softcap", 20: "gemm_tcgen05", 30: "attn_prefill_tc", 40: "latent_prepare",
                       41: "latent_attn_generic", 42: "gate_heads", 43: "latent_attn_mma", 44: "latent_attn_join",
-                      50: "moe_route", 51: "moe_plan", 52: "moe_grouped", 53: "moe_gather", 54: "moe_combine", 55: "moe_skinny", 56: "moe_skinny_mma"}
+                      50: "moe_route", 51: "moe_plan", 52: "moe_grouped", 53: "moe_gather", 54: "moe_combine", 55: "moe_skinny", 56: "moe_skinny_mma", 57: "moe_rank", 58: "moe_offsets", 59: "moe_place"}
 
 
 def set_trace(buf: Optional[torch.Tensor], count: Optional[torch.Tensor]) -> None:
@@ -871,13 +872,19 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_up: tor
     mma_rows = 16 if (32 * max(d, ff) <= 72 * 1024 and slots > 4 * E) else 8
     BM = (mma_rows if skinny_mma else 8) if skinny else (64 if slots >= 32 * E else 16)
     max_tiles = min(slots, slots // BM + E)
-    meta = torch.empty((2 * slots + E + 1 + 3 * max_tiles + 1,), dtype=torch.int32, device=dev)
+    many = slots > 2048                   # the plan in three kernels over all SMs (needs counters and ranks)
+    meta = torch.empty((2 * slots + E + 1 + 3 * max_tiles + 1 + (E + slots if many else 0),), dtype=torch.int32, device=dev)
     perm, inv = meta[:slots], meta[slots:2 * slots]
     offsets = meta[2 * slots:2 * slots + E + 1]
     tiles = meta[2 * slots + E + 1:2 * slots + E + 1 + 3 * max_tiles]
-    n_tiles = meta[-1:]
+    at = 2 * slots + E + 1 + 3 * max_tiles
+    n_tiles = meta[at:at + 1]
+    counts, rank = (meta[at + 1:at + 1 + E], meta[at + 1 + E:]) if many else (None, None)
     _check(lib.bspec_moe_plan(ids.data_ptr(), slots, E, BM, perm.data_ptr(), inv.data_ptr(), offsets.data_ptr(),
-                              tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, _stream()), "moe_plan")
+                              tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, _ptr(counts), _ptr(rank), _stream()),
+           "moe_plan")
+    if many:
+        count_launches(2)
     if library:
         rows = torch.empty((slots, d), dtype=h.dtype, device=dev)
         _check(lib.bspec_moe_gather(h.data_ptr(), code, perm.data_ptr(), top, rows.data_ptr(), slots, d, _stream()),

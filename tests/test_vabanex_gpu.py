@@ -251,6 +251,10 @@ LATENT_SHAPES = [
     (128, 512, 64, 64, [1, 2], [700, 65]),
     (20, 256, 64, 32, [129], [385]),
     (7, 64, 16, 8, [33, 1], [33, 2049]),
+    (5, 48, 16, 8, [9, 1], [40, 200]),                 # a latent of 3 x 16: an odd number of output tiles per warp
+    (3, 80, 48, 16, [70], [70]),
+    (2, 96, 16, 16, [1, 1, 1], [5, 130, 64]),          # decode with a latent of 3 x 32
+    (32, 160, 32, 16, [1, 1], [300, 31]),
 ]
 
 
@@ -388,7 +392,7 @@ def _check_routing(h, w, ids, wts, E, G, keep, top, n, dtype):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n,E,top,d,ff", [(1, 4, 2, 32, 24), (9, 6, 3, 100, 36), (300, 8, 4, 64, 40), (40, 16, 1, 72, 8),
                                           (8, 64, 6, 512, 136), (64, 32, 4, 264, 1032), (8, 64, 6, 512, 160),
-                                          (64, 16, 4, 288, 1056), (3, 8, 2, 2048, 96)])
+                                          (64, 16, 4, 288, 1056), (3, 8, 2, 2048, 96), (700, 8, 4, 64, 40)])
 def test_routed_experts(ops, dtype, n, E, top, d, ff):
     g = torch.Generator(device=DEV).manual_seed(n)
     h = torch.randn(n, d, device=DEV, generator=g).to(dtype)
