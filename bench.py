@@ -310,7 +310,7 @@ def vabanex_config_json(z, layers, vocab=32000):
                router=dict(experts=z["experts"], top=z["top"], scale=2.5, groups=dict(count=z["groups"], keep=z["keep"])))
     dense = dict(kind="dense", ff=z["dense_ff"], limit=7.0)
     return dict(architecture="Vabanex", vocab=vocab, width=z["width"], embedding=dict(scale=1.0), norm=dict(eps=1e-5),
-                logit_softcap=30.0,
+                logit_softcap=50.0,
                 layers=[dict(type="latent_attention", mixer=mixer, mlp=dense if i == 0 else moe) for i in range(layers)])
 
 
