@@ -17,6 +17,7 @@
 // shares in their order.  How the tiles are cut into shares follows from the request's length, read on the device.
 #include "common.cuh"
 #include <math.h>
+#include <stdlib.h>
 using namespace bspec;
 
 namespace {
@@ -50,14 +51,16 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-__host__ __device__ inline size_t smem_bytes(int D, int BM) {
+__host__ __device__ inline size_t smem_bytes(int D, int BM, int stages = 2) {
   const int DP = D + 8;
-  return (size_t)(BM + 2 * BN) * DP * 2 + (size_t)BM * (BN + 8) * 4 + 2 * (size_t)BM * (BN + 8) * 2 + 3 * BM * 4;
+  return (size_t)(BM + stages * BN) * DP * 2 + (size_t)BM * (BN + 8) * 4 + 2 * (size_t)BM * (BN + 8) * 2 + 3 * BM * 4;
 }
 
 // RG row groups x CH column groups of warps; NT: n-tiles (of 8 columns) of the output one warp may own,
 // R / (8 CH) <= NT.
-template <int RG, int CH, int NT>
+// ST: tiles of entries in shared memory: 2 (the next one arrives under the current one's products) or 1 (two CTAs
+// share an SM instead and cover each other's loads).
+template <int RG, int CH, int NT, int ST = 2>
 __global__ void __launch_bounds__(32 * RG * CH)
 latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, long long ql_head,
                        const __nv_bfloat16* __restrict__ qr, long long qr_row, long long qr_head,
@@ -76,7 +79,7 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
   constexpr int PP = BN + 8, SP = BN + 8;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* Ks = Qs + (size_t)BM * DP;
-  float* Ss = reinterpret_cast<float*>(Ks + (size_t)2 * BN * DP);
+  float* Ss = reinterpret_cast<float*>(Ks + (size_t)ST * BN * DP);
   __nv_bfloat16* Ph = reinterpret_cast<__nv_bfloat16*>(Ss + (size_t)BM * SP);
   __nv_bfloat16* Pl = Ph + (size_t)BM * PP;
   float* row_m = reinterpret_cast<float*>(Pl + (size_t)BM * PP);
@@ -205,12 +208,14 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
   cp_async_commit();
   ahead = lookup(t_begin + 1);
   for (int tile = t_begin; tile < t_end; ++tile) {
-    const int buf = (tile - t_begin) & 1;
+    const int buf = ST == 2 ? (tile - t_begin) & 1 : 0;
     cp_async_wait<0>();
     __syncthreads();                              // the tile is here, and everybody is done with the tile before
-    if (tile + 1 < t_end) load_tile(buf ^ 1, ahead);
-    cp_async_commit();
-    ahead = lookup(tile + 2);
+    if (ST == 2) {
+      if (tile + 1 < t_end) load_tile(buf ^ 1, ahead);
+      cp_async_commit();
+      ahead = lookup(tile + 2);
+    }
     // ---- S: this warp's 16 rows x KW keys, two accumulator sets over alternating k steps
     {
       constexpr int NS = KW / 8;
@@ -335,6 +340,12 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
         }
       }
     }
+    if (ST == 1) {                                // the one buffer is free once every warp has left the tile
+      __syncthreads();
+      if (tile + 1 < t_end) load_tile(0, ahead);
+      cp_async_commit();
+      ahead = lookup(tile + 2);
+    }
   }
   cp_async_wait<0>();
   __syncthreads();          // row_m / row_l of the init (no tiles) or of the last tile, for every warp
@@ -422,13 +433,28 @@ BSPEC_API int bspec_latent_attention_mma_supported(int R, int P) {
   return (R > 0 && R % 16 == 0 && P >= 16 && P % 16 == 0 && R <= 512 && smem_bytes(R + P, 64) <= 220 * 1024) ? 1 : 0;
 }
 
+// How prompt portions are tiled: 2 (default) = 32 rows, 8 warps, one tile of entries, two CTAs per SM, when those
+// fit (else as 0); 0 = 64 rows, 16 warps, two tiles of entries in flight; 1 = 64 rows, 8 warps.  Measured on a
+// 4,096-token prompt with 16 / 32 heads, latent 512 + 64: 127 / 134, 118 / 126 and 110 / 116 TFLOP/s.  The
+// environment variable is a tuning switch.
+static int prompt_mode() {
+  static const int mode = [] {
+    const char* e = getenv("BSPEC_LATENT_PROMPT");
+    return e != nullptr ? atoi(e) : 2;
+  }();
+  return mode;
+}
+static bool two_small_ctas(int R, int P) {
+  return prompt_mode() == 2 && R % 32 == 0 && smem_bytes(R + P, 32, 1) <= 112 * 1024;
+}
+
 // Rows per CTA for a step whose longest portion has max_q_len tokens: 16 or 32 when every request's (token, head)
 // rows fit (decoded tokens of models with few heads; needs a latent that is a multiple of 32), else 64.
-BSPEC_API int bspec_latent_attention_mma_rows(int max_q_len, int H, int R) {
+BSPEC_API int bspec_latent_attention_mma_rows(int max_q_len, int H, int R, int P) {
   const long long rows = (long long)max_q_len * H;
   if (R % 32 == 0 && rows <= 16) return 16;
   if (R % 32 == 0 && rows <= 32) return 32;
-  return 64;
+  return two_small_ctas(R, P) ? 32 : 64;
 }
 
 BSPEC_API int bspec_latent_attention_mma(const void* ql, long long ql_row, long long ql_head, const void* qr,
@@ -439,14 +465,16 @@ BSPEC_API int bspec_latent_attention_mma(const void* ql, long long ql_row, long 
                                          int page_size, float scale, int n_splits, float* o_part, float* ml_part,
                                          long long n_pages, const float* inv_freq, float magnitude,
                                          cudaStream_t stream) {
+  const bool wide = prompt_mode() != 1;
   if (n_entries <= 0 || max_q_len <= 0) return 0;
   if (!bspec_latent_attention_mma_supported(R, P) || n_splits < 1 || (n_splits > 1 && (!o_part || !ml_part)))
     return (int)cudaErrorInvalidValue;
-  const int BM = bspec_latent_attention_mma_rows(max_q_len, H, R);
+  const int BM = bspec_latent_attention_mma_rows(max_q_len, H, R, P);
+  const bool small_pair = BM == 32 && (long long)max_q_len * H > 32;     // prompt portions on 32-row tiles, one buffer
   const long long row_tiles = ((long long)max_q_len * H + BM - 1) / BM;
   if ((long long)max_q_len * H > 2147483647ll || n_entries > 65535 || n_splits > 64) return (int)cudaErrorInvalidConfiguration;
   dim3 grid((unsigned)row_tiles, n_entries, n_splits);
-  const size_t smem = smem_bytes(R + P, BM);
+  const size_t smem = smem_bytes(R + P, BM, small_pair ? 1 : 2);
 #define LM(RG, CH, N)                                                                                                \
   do {                                                                                                               \
     cudaFuncSetAttribute(latent_attn_mma_kernel<RG, CH, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
@@ -455,7 +483,22 @@ BSPEC_API int bspec_latent_attention_mma(const void* ql, long long ql_row, long 
                  (const __nv_bfloat16*)cache, qo_indptr, positions, kv_indptr, kv_indices, H, R, P, page_size,       \
                  scale, n_splits, o_part, ml_part, n_pages, inv_freq, magnitude);                                    \
   } while (0)
-  if (BM == 64) {
+#define LM1(RG, CH, N)                                                                                               \
+  do {                                                                                                               \
+    cudaFuncSetAttribute(latent_attn_mma_kernel<RG, CH, N, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    BSPEC_LAUNCH((latent_attn_mma_kernel<RG, CH, N, 1>), grid, 32 * RG * CH, smem, stream, (const __nv_bfloat16*)ql, \
+                 ql_row, ql_head, (const __nv_bfloat16*)qr, qr_row, qr_head, (__nv_bfloat16*)out, o_row, o_head,     \
+                 (const __nv_bfloat16*)cache, qo_indptr, positions, kv_indptr, kv_indices, H, R, P, page_size,       \
+                 scale, n_splits, o_part, ml_part, n_pages, inv_freq, magnitude);                                    \
+  } while (0)
+  if (small_pair) {
+    const int ntw = R / 32;
+    if (ntw <= 4) LM1(2, 4, 4); else if (ntw <= 8) LM1(2, 4, 8); else LM1(2, 4, 16);
+  } else if (BM == 64 && R % 32 == 0 && wide) {
+    // sixteen warps: twice the warps to hide the latencies of the same tile (a warp owns a quarter of the columns)
+    const int ntw = R / 32;
+    if (ntw <= 4) LM(4, 4, 4); else if (ntw <= 8) LM(4, 4, 8); else LM(4, 4, 16);
+  } else if (BM == 64) {
     const int ntw = R / 16;
     if (ntw <= 8) LM(4, 2, 8); else if (ntw <= 16) LM(4, 2, 16); else LM(4, 2, 32);
   } else {
@@ -463,6 +506,7 @@ BSPEC_API int bspec_latent_attention_mma(const void* ql, long long ql_row, long 
     if (BM == 16) { if (ntw <= 4) LM(1, 4, 4); else if (ntw <= 8) LM(1, 4, 8); else LM(1, 4, 16); }
     else { if (ntw <= 4) LM(2, 4, 4); else if (ntw <= 8) LM(2, 4, 8); else LM(2, 4, 16); }
   }
+#undef LM1
 #undef LM
   int err = BSPEC_LAUNCH_CHECK();
   if (err != 0 || n_splits == 1) return err;

@@ -59,7 +59,7 @@ _SIGNATURES = {
                                        c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_void_p],
     "bspec_latent_attention_mma_supported": [c_int, c_int],
-    "bspec_latent_attention_mma_rows": [c_int, c_int, c_int],
+    "bspec_latent_attention_mma_rows": [c_int, c_int, c_int, c_int],
     "bspec_latent_attention_mma": [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p,
                                    c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                    c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_longlong,
@@ -773,7 +773,7 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor
         # Few rows and many entries (decode): the key tiles of a request are cut into shares for more CTAs.  The
         # count depends on the step's shape alone (entries, longest portion, longest allowed request), so a
         # captured step keeps it; shares that get no tile leave at once.
-        rows = lib.bspec_latent_attention_mma_rows(ctx.max_q_len, n_heads, kv_rank)       # rows of a CTA's tile
+        rows = lib.bspec_latent_attention_mma_rows(ctx.max_q_len, n_heads, kv_rank, rot_dim)       # rows of a CTA's tile
         row_tiles = -(-(ctx.max_q_len * n_heads) // rows)
         n_splits = 1
         if ctx.max_q_len * n_heads <= 256:
