@@ -444,6 +444,18 @@ static int prompt_mode() {
   }();
   return mode;
 }
+// Decoded tokens (16- and 32-row tiles): 1 (default) = one tile of entries per CTA, so that four CTAs share an SM;
+// 2 = two tiles in flight per CTA, two CTAs per SM.
+static int decode_stages() {
+  static const int st = [] {
+    const char* e = getenv("BSPEC_LATENT_DECODE_STAGES");
+    return e != nullptr && atoi(e) == 2 ? 2 : 1;
+  }();
+  return st;
+}
+BSPEC_API int bspec_latent_attention_mma_smem(int rows, int R, int P, int prompt) {
+  return (int)smem_bytes(R + P, rows, (rows == 64 || (rows < 64 && !prompt && decode_stages() == 2)) ? 2 : 1);
+}
 static bool two_small_ctas(int R, int P) {
   return prompt_mode() == 2 && R % 32 == 0 && smem_bytes(R + P, 32, 1) <= 112 * 1024;
 }
@@ -474,7 +486,8 @@ BSPEC_API int bspec_latent_attention_mma(const void* ql, long long ql_row, long 
   const long long row_tiles = ((long long)max_q_len * H + BM - 1) / BM;
   if ((long long)max_q_len * H > 2147483647ll || n_entries > 65535 || n_splits > 64) return (int)cudaErrorInvalidConfiguration;
   dim3 grid((unsigned)row_tiles, n_entries, n_splits);
-  const size_t smem = smem_bytes(R + P, BM, small_pair ? 1 : 2);
+  const bool one_stage = small_pair || (BM < 64 && decode_stages() == 1);
+  const size_t smem = smem_bytes(R + P, BM, one_stage ? 1 : 2);
 #define LM(RG, CH, N)                                                                                                \
   do {                                                                                                               \
     cudaFuncSetAttribute(latent_attn_mma_kernel<RG, CH, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
@@ -501,6 +514,10 @@ BSPEC_API int bspec_latent_attention_mma(const void* ql, long long ql_row, long 
   } else if (BM == 64) {
     const int ntw = R / 16;
     if (ntw <= 8) LM(4, 2, 8); else if (ntw <= 16) LM(4, 2, 16); else LM(4, 2, 32);
+  } else if (one_stage) {
+    const int ntw = R / 32;
+    if (BM == 16) { if (ntw <= 4) LM1(1, 4, 4); else if (ntw <= 8) LM1(1, 4, 8); else LM1(1, 4, 16); }
+    else { if (ntw <= 4) LM1(2, 4, 4); else if (ntw <= 8) LM1(2, 4, 8); else LM1(2, 4, 16); }
   } else {
     const int ntw = R / 32;
     if (BM == 16) { if (ntw <= 4) LM(1, 4, 4); else if (ntw <= 8) LM(1, 4, 8); else LM(1, 4, 16); }

@@ -60,6 +60,7 @@ _SIGNATURES = {
                                        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_void_p],
     "bspec_latent_attention_mma_supported": [c_int, c_int],
     "bspec_latent_attention_mma_rows": [c_int, c_int, c_int, c_int],
+    "bspec_latent_attention_mma_smem": [c_int, c_int, c_int, c_int],
     "bspec_latent_attention_mma": [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p,
                                    c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                    c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_longlong,
@@ -778,8 +779,8 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor
         n_splits = 1
         if ctx.max_q_len * n_heads <= 256:
             # as many shares as fill the CTAs that are resident at once (one wave), at least 256 keys each
-            smem = (rows + 64) * (kv_rank + rot_dim + 8) * 2 + rows * 330
-            slots = sm_count(q_lat.device) * max(1, min(4, (220 * 1024) // smem))
+            smem = lib.bspec_latent_attention_mma_smem(rows, kv_rank, rot_dim, 0) + 1024
+            slots = sm_count(q_lat.device) * max(1, min(4, (227 * 1024) // smem))
             n_splits = max(1, min(64, slots // (ctx.n_entries * row_tiles), -(-ctx.max_kv_len // 256)))
         o_part = ml_part = None
         if n_splits > 1:
