@@ -12,7 +12,10 @@
 // The warps of a row group meet at a barrier of their own between these phases (the row groups drift apart, so
 // one's softmax runs under another's products); the whole CTA meets once per tile, when the next tile has landed.
 //
-// Entries arrive by cp.async, two tiles in flight.  With n_splits > 1 (decode: few rows, many entries) CTA z takes
+// Entries arrive by cp.async; the block-table lookup of a tile is made one tile before its copies.  A CTA holds
+// two tiles of entries (the next one arrives under the current one's products: the 64-row tiles) or one (32-row
+// tiles of prompt portions and the 16- and 32-row tiles of decoded tokens: two to four CTAs then share an SM and
+// cover each other's loads, which measured faster).  With n_splits > 1 (decode: few rows, many entries) CTA z takes
 // the z-th share of the key tiles and leaves (max, sum, unnormalised output) for the join kernel, which adds the
 // shares in their order.  How the tiles are cut into shares follows from the request's length, read on the device.
 #include "common.cuh"

@@ -177,10 +177,13 @@ moe_rank_kernel(const int* __restrict__ ids, int slots, int* __restrict__ counts
 __global__ void moe_offsets_kernel(const int* __restrict__ counts, int E, int BM, int* __restrict__ offsets,
                                    int* __restrict__ tiles, int* __restrict__ n_tiles_out, int max_tiles) {
   bspec::pdl_prologue(58);
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  __shared__ int cnt[MAX_EXPERTS];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = counts[e];      // one round trip for all counts
+  __syncthreads();
+  if (threadIdx.x != 0) return;
   int run = 0, nt = 0;
   for (int e = 0; e < E; ++e) {
-    const int c = counts[e];
+    const int c = cnt[e];
     offsets[e] = run;
     for (int r = 0; r < c && nt < max_tiles; r += BM) {
       tiles[3 * nt] = e;
@@ -496,7 +499,7 @@ BSPEC_API int bspec_moe_plan(const int* ids, int slots, int E, int BM, int* perm
   if (err != cudaSuccess) return (int)err;
   const int blocks = (slots + 255) / 256;
   BSPEC_LAUNCH((moe_rank_kernel), blocks, 256, 0, stream, ids, slots, counts, rank);
-  BSPEC_LAUNCH((moe_offsets_kernel), 1, 32, 0, stream, (const int*)counts, E, BM, offsets, tiles, n_tiles, max_tiles);
+  BSPEC_LAUNCH((moe_offsets_kernel), 1, 256, 0, stream, (const int*)counts, E, BM, offsets, tiles, n_tiles, max_tiles);
   BSPEC_LAUNCH((moe_place_kernel), blocks, 256, 0, stream, ids, (const int*)rank, (const int*)offsets, slots, perm, inv);
   return BSPEC_LAUNCH_CHECK();
 }

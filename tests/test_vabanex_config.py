@@ -68,3 +68,38 @@ def test_router_by_hand():
     assert sorted(ids[0].tolist()) == [0, 4, 5]
     got = dict(zip(ids[0].tolist(), wt[0].tolist()))
     assert got[5] == pytest.approx(0.9) and got[4] == pytest.approx(1.0) and got[0] == pytest.approx(1.8)
+
+
+def _tiny_model(seed=3):
+    g = torch.Generator().manual_seed(seed)
+    cfg = copy.deepcopy(CFG)
+    model = get_model(config_from_json_dict(cfg), Runtime(torch.float32, torch.device("cpu")))
+    w = {}
+    for name, spec in model.param_specs().items():
+        t = torch.randn(spec.shape, generator=g, dtype=torch.float64) * (0.2 if len(spec.shape) > 1 else 0.1)
+        w[name] = t + 1.0 if spec.init == "ones_normal" else t
+    return cfg, w
+
+
+def test_plain_implementation_is_causal_and_position_aware():
+    """Properties the oracle must have whatever its weights: a later token changes no earlier logits; the same
+    token at another position gives other logits (the rotation acts); the soft cap bounds the logits."""
+    cfg, w = _tiny_model()
+    toks = [5, 17, 3, 250, 99, 17, 8, 64, 1, 2, 33]
+    base = P.forward(cfg, w, toks)
+    other = P.forward(cfg, w, toks[:6] + [77] + toks[7:])
+    assert torch.equal(base[:6], other[:6]) and not torch.allclose(base[6:], other[6:])
+    assert not torch.allclose(base[1], base[5])                  # token 17 at positions 1 and 5
+    assert base.abs().max() < cfg["logit_softcap"]
+    layers = []
+    P.forward(cfg, w, toks, layers)
+    assert len(layers) == 3 and layers[0].shape == (len(toks), cfg["width"])
+
+
+def test_rotation_keeps_pairs_lengths_times_the_magnitude():
+    f, mag = P.yarn_frequencies(MIXER["rot"])
+    assert mag == pytest.approx(0.1 * torch.log(torch.tensor(8.0)).item() + 1.0)
+    x = torch.randn(7, 8, dtype=torch.float64)
+    y = P.rotate_pairs(x, torch.arange(7) * 13, f, mag)
+    assert torch.allclose((y[:, 0::2] ** 2 + y[:, 1::2] ** 2), mag ** 2 * (x[:, 0::2] ** 2 + x[:, 1::2] ** 2))
+    assert torch.allclose(y[0], x[0] * mag)                      # position 0 rotates by nothing
