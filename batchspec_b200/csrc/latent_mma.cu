@@ -229,29 +229,40 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
         for (int y = 0; y < NS; ++y) s[x][y][0] = s[x][y][1] = s[x][y][2] = s[x][y][3] = 0.f;
       const uint32_t kb = kb_s + (uint32_t)buf * (uint32_t)(BN * DP * 2);
       const int nks = D / 16;
-      auto step = [&](float (&acc)[NS][4], uint32_t off) {       // off: bytes along the row, 32 per k step
-        uint32_t a[4];
-        ldsm_x4(a, qa_s + off);
+      // The asm statements keep their order, so the loop is pipelined by hand: the fragments of k step i + 1 are
+      // fetched before the products of step i are issued (two sets of fragment registers, four accumulator chains).
+      uint32_t fa[2][4], fb[2][4];
+      auto fetch = [&](int slot, uint32_t off) {                 // off: bytes along the row, 32 per k step
+        ldsm_x4(fa[slot], qa_s + off);
         if (KW == 16) {
-          uint32_t b[4];
-          ldsm_x4(b, kb + off);
-          mma_bf16(acc[0], a, b[0], b[1]);
-          mma_bf16(acc[NS - 1], a, b[2], b[3]);
+          ldsm_x4(fb[slot], kb + off);
         } else {
-          uint32_t b[2];
-          ldsm_x2(b, kb + off);
-          mma_bf16(acc[0], a, b[0], b[1]);
+          uint32_t t[2];
+          ldsm_x2(t, kb + off);
+          fb[slot][0] = t[0];
+          fb[slot][1] = t[1];
         }
       };
+      auto mul = [&](float (&acc)[NS][4], int slot) {
+        mma_bf16(acc[0], fa[slot], fb[slot][0], fb[slot][1]);
+        if (KW == 16) mma_bf16(acc[NS - 1], fa[slot], fb[slot][2], fb[slot][3]);
+      };
+      fetch(0, 0u);
       int ks = 0;
-      for (; ks + 3 < nks; ks += 4) {              // four independent chains
-        const uint32_t off = 32u * ks;
-        step(s[0], off);
-        step(s[1], off + 32);
-        step(s[2], off + 64);
-        step(s[3], off + 96);
+      for (; ks + 4 <= nks; ks += 4) {
+        fetch(1, 32u * (ks + 1));
+        mul(s[0], 0);
+        fetch(0, 32u * (ks + 2));
+        mul(s[1], 1);
+        fetch(1, 32u * (ks + 3));
+        mul(s[2], 0);
+        if (ks + 4 < nks) fetch(0, 32u * (ks + 4));
+        mul(s[3], 1);
       }
-      for (; ks < nks; ++ks) step(s[0], 32u * ks);
+      for (; ks < nks; ++ks) {
+        mul(s[0], 0);
+        if (ks + 1 < nks) fetch(0, 32u * (ks + 1));
+      }
 #pragma unroll
       for (int y = 0; y < NS; ++y)
 #pragma unroll
@@ -330,15 +341,17 @@ latent_attn_mma_kernel(const __nv_bfloat16* __restrict__ ql, long long ql_row, l
         ldsm_x4(ah, ph_s + 32 * kk);
         ldsm_x4(al, pl_s + 32 * kk);
         const uint32_t vk = vt + (uint32_t)kk * (uint32_t)(16 * DP * 2);
+        uint32_t vb[2][4];                         // the value fragments, fetched one pair of tiles ahead
+        ldsm_x4_trans(vb[0], vk);
 #pragma unroll
         for (int nd = 0; nd < NT; nd += 2) {
           if (nd < ntw) {
-            uint32_t b[4];
-            ldsm_x4_trans(b, vk + 16 * nd);
-            mma_bf16(o[nd], ah, b[0], b[1]);
-            if (nd + 1 < ntw) mma_bf16(o[nd + 1], ah, b[2], b[3]);
-            mma_bf16(o[nd], al, b[0], b[1]);
-            if (nd + 1 < ntw) mma_bf16(o[nd + 1], al, b[2], b[3]);
+            const int cur = (nd >> 1) & 1;
+            if (nd + 2 < ntw) ldsm_x4_trans(vb[cur ^ 1], vk + 16 * (nd + 2));
+            mma_bf16(o[nd], ah, vb[cur][0], vb[cur][1]);
+            if (nd + 1 < ntw) mma_bf16(o[nd + 1], ah, vb[cur][2], vb[cur][3]);
+            mma_bf16(o[nd], al, vb[cur][0], vb[cur][1]);
+            if (nd + 1 < ntw) mma_bf16(o[nd + 1], al, vb[cur][2], vb[cur][3]);
           }
         }
       }
