@@ -8,7 +8,8 @@ Here all bookkeeping is on the host: a pool is a LIFO free list shared by all
 requests, a request holds ceil(len / page_size) table entries per group (none when
 empty), finished requests' pages go back to the list and are handed out again, and
 a windowed group also gives back pages that the window has passed (their table
-entries become -1; no kernel reads them).
+entries become -1; no kernel reads them), and a chunked group the pages before the
+chunk that the next position falls into.
 
 The pool is zeroed once when it is made and never again: what a kernel loads past a request's length is
 masked, it only has to be finite.
@@ -236,7 +237,7 @@ class CacheManager:
         for g in self.groups:
             ps = g.page_size
             n = -(-total_len // ps)
-            if g.spec.policy == "window":
+            if g.spec.policy in ("window", "chunk"):
                 n = min(n, (g.spec.window - 1 + max(1, portion) + ps - 1) // ps + 1)
             out.append(n)
         return out
@@ -277,14 +278,18 @@ class CacheManager:
 
     def commit(self, req_id, n_new: int) -> None:
         """The step wrote n_new tokens: grow the length and give back pages that a
-        window has passed (every later query reads keys >= length - window + 1)."""
+        window has passed (every later query reads keys >= length - window + 1) or that
+        lie before the chunk of every later query."""
         rc = self.requests[req_id]
         rc.length += n_new
         for g, table in zip(self.groups, rc.tables):
             assert len(table) == -(-rc.length // g.page_size), "block table out of step"
-            if g.spec.policy != "window":
+            if g.spec.policy == "window":
+                first_needed = max(0, rc.length - g.spec.window + 1)
+            elif g.spec.policy == "chunk":
+                first_needed = (rc.length // g.spec.window) * g.spec.window      # start of the next position's chunk
+            else:
                 continue
-            first_needed = max(0, rc.length - g.spec.window + 1)
             dead = first_needed // g.page_size             # pages wholly before first_needed
             gone = [p for p in table[:dead] if p >= 0]
             if gone:

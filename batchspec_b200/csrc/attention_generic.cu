@@ -6,7 +6,12 @@
 // key index, so the order of every sum depends only on the query's own position,
 // not on how the request was cut into steps or on what else is in the batch.
 //
-// Cache layer layout: [pages][2 (k, v)][Hkv][page_size][hd].
+// Cache layer layout: [pages][k: [Hkv][page_size][hd] | v: [Hkv][page_size][vd]] (vd = hd unless values have a size
+// of their own).
+//
+// Masks: causal; ``window`` > 0 keeps the last ``window`` keys; ``chunk`` > 0 keeps the keys of the query's own
+// chunk, floor(key / chunk) == floor(query / chunk), chunks counted from position 0 of the request.  ``sink``: one
+// float32 per query head that joins the softmax denominator as exp(sink) and has no value.
 #include "common.cuh"
 #include <math.h>
 using namespace bspec;
@@ -21,7 +26,7 @@ attn_generic_kernel(const T* __restrict__ q, long long q_row_stride, T* __restri
                     const T* __restrict__ cache, const int* __restrict__ qo_indptr,
                     const int* __restrict__ positions, const int* __restrict__ kv_indptr,
                     const int* __restrict__ kv_indices, int Hq, int Hkv, int hd, int page_size, float scale,
-                    int window, long long n_pages) {
+                    int window, long long n_pages, int vd, int chunk, const float* __restrict__ sink) {
   bspec::pdl_prologue(7);
   __shared__ float qs[WARPS][MAX_HD];
   const int e = blockIdx.y, h = blockIdx.z;
@@ -40,9 +45,11 @@ attn_generic_kernel(const T* __restrict__ q, long long q_row_stride, T* __restri
   if (!active) return;
   const int pos = positions[t];
   const int hi = pos;                                   // last visible key (inclusive)
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  if (chunk > 0) lo = max(lo, (pos / chunk) * chunk);
   const int* table = kv_indices + kv_indptr[e];
-  const size_t page_elems = (size_t)Hkv * page_size * hd;
+  const size_t k_elems = (size_t)Hkv * page_size * hd;          // the keys of a page; its values follow them
+  const size_t page_elems = k_elems + (size_t)Hkv * page_size * vd;
   const size_t head_off = (size_t)kvh * page_size * hd;
   constexpr int ND = MAX_HD / 32;
   float acc[ND];
@@ -52,12 +59,13 @@ attn_generic_kernel(const T* __restrict__ q, long long q_row_stride, T* __restri
   for (int kb = (lo / 32) * 32; kb <= hi; kb += 32) {
     const int key = kb + lane;
     bool valid = key >= lo && key <= hi;
-    long long koff = 0;
+    long long koff = 0, voff = 0;
     float s = -INFINITY;
     if (valid && !bspec::in_range(table[key / page_size], n_pages, 107)) valid = false;
     if (valid) {
       const int page = table[key / page_size];
-      koff = (long long)((size_t)page * 2 * page_elems + head_off + (size_t)(key % page_size) * hd);
+      koff = (long long)((size_t)page * page_elems + head_off + (size_t)(key % page_size) * hd);
+      voff = (long long)((size_t)page * page_elems + k_elems + ((size_t)kvh * page_size + (size_t)(key % page_size)) * vd);
       const T* kp = cache + koff;
       float dot = 0.f;
       for (int d = 0; d < hd; ++d) dot += qs[warp][d] * to_f32(kp[d]);
@@ -72,47 +80,180 @@ attn_generic_kernel(const T* __restrict__ q, long long q_row_stride, T* __restri
     const int nk = min(32, hi - kb + 1);
     for (int kk = 0; kk < nk; ++kk) {
       const float pk = __shfl_sync(0xffffffffu, p, kk);
-      const long long off = __shfl_sync(0xffffffffu, koff, kk);
+      const long long off = __shfl_sync(0xffffffffu, voff, kk);
       if (pk != 0.f) {
-        const T* vp = cache + off + page_elems;
+        const T* vp = cache + off;
 #pragma unroll
         for (int i = 0; i < ND; ++i) {
           const int d = lane + 32 * i;
-          if (d < hd) acc[i] += pk * to_f32(vp[d]);
+          if (d < vd) acc[i] += pk * to_f32(vp[d]);
         }
       }
     }
     m = m_new;
   }
+  if (sink != nullptr) {                                // one more term of the denominator, without a value
+    const float sk = sink[h];
+    const float m_new = fmaxf(m, sk);
+    const float corr = expf(m - m_new);
+    l = l * corr + expf(sk - m_new);
+#pragma unroll
+    for (int i = 0; i < ND; ++i) acc[i] *= corr;
+  }
   const float inv = 1.f / l;
-  T* op = out + ((size_t)t * Hq + h) * hd;
+  T* op = out + ((size_t)t * Hq + h) * vd;
 #pragma unroll
   for (int i = 0; i < ND; ++i) {
     const int d = lane + 32 * i;
-    if (d < hd) op[d] = from_f32<T>(acc[i] * inv);
+    if (d < vd) op[d] = from_f32<T>(acc[i] * inv);
   }
 }
 }  // namespace
 
 // q: rows of row stride q_row_stride (elements), heads packed [Hq][hd] at the row start.
-// out: [n, Hq*hd].  max_q_len: the longest request portion in the step (sizes the grid).
-BSPEC_API int bspec_attention_generic(const void* q, long long q_row_stride, void* out, const void* cache, int dtype,
-                                      const int* qo_indptr, const int* positions, const int* kv_indptr,
-                                      const int* kv_indices, int n_entries, int max_q_len, int Hq, int Hkv, int hd,
-                                      int page_size, float scale, int window, long long n_pages,
-                                      cudaStream_t stream) {
+// out: [n, Hq*vd].  max_q_len: the longest request portion in the step (sizes the grid).
+static int launch_attention_generic(const void* q, long long q_row_stride, void* out, const void* cache, int dtype,
+                                    const int* qo_indptr, const int* positions, const int* kv_indptr,
+                                    const int* kv_indices, int n_entries, int max_q_len, int Hq, int Hkv, int hd,
+                                    int page_size, float scale, int window, long long n_pages, int vd, int chunk,
+                                    const float* sink, cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return 0;
-  if (hd > MAX_HD || hd <= 0 || Hq % Hkv != 0) return (int)cudaErrorInvalidValue;
+  if (hd > MAX_HD || hd <= 0 || vd > MAX_HD || vd <= 0 || Hq % Hkv != 0) return (int)cudaErrorInvalidValue;
   dim3 grid((max_q_len + WARPS - 1) / WARPS, n_entries, Hq);
   if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidConfiguration;
   if (dtype == BSPEC_F32)
     BSPEC_LAUNCH((attn_generic_kernel<float>), grid, WARPS * 32, 0, stream, 
         (const float*)q, q_row_stride, (float*)out, (const float*)cache, qo_indptr, positions, kv_indptr, kv_indices,
-        Hq, Hkv, hd, page_size, scale, window, n_pages);
+        Hq, Hkv, hd, page_size, scale, window, n_pages, vd, chunk, sink);
   else
     BSPEC_LAUNCH((attn_generic_kernel<__nv_bfloat16>), grid, WARPS * 32, 0, stream, 
         (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache, qo_indptr, positions,
-        kv_indptr, kv_indices, Hq, Hkv, hd, page_size, scale, window, n_pages);
+        kv_indptr, kv_indices, Hq, Hkv, hd, page_size, scale, window, n_pages, vd, chunk, sink);
+  return BSPEC_LAUNCH_CHECK();
+}
+
+BSPEC_API int bspec_attention_generic(const void* q, long long q_row_stride, void* out, const void* cache, int dtype,
+                                      const int* qo_indptr, const int* positions, const int* kv_indptr,
+                                      const int* kv_indices, int n_entries, int max_q_len, int Hq, int Hkv, int hd,
+                                      int page_size, float scale, int window, long long n_pages,
+                                      cudaStream_t stream) {
+  return launch_attention_generic(q, q_row_stride, out, cache, dtype, qo_indptr, positions, kv_indptr, kv_indices,
+                                  n_entries, max_q_len, Hq, Hkv, hd, page_size, scale, window, n_pages, hd, 0, nullptr,
+                                  stream);
+}
+
+// The same with values of their own size ``vd``, a chunk mask (0: none) and a sink per query head (null: none).
+BSPEC_API int bspec_attention_masked(const void* q, long long q_row_stride, void* out, const void* cache, int dtype,
+                                     const int* qo_indptr, const int* positions, const int* kv_indptr,
+                                     const int* kv_indices, int n_entries, int max_q_len, int Hq, int Hkv, int hd,
+                                     int vd, int page_size, float scale, int window, int chunk, const float* sink,
+                                     long long n_pages, cudaStream_t stream) {
+  return launch_attention_generic(q, q_row_stride, out, cache, dtype, qo_indptr, positions, kv_indptr, kv_indices,
+                                  n_entries, max_q_len, Hq, Hkv, hd, page_size, scale, window, n_pages, vd, chunk, sink,
+                                  stream);
+}
+
+// ---------------------------------------------------------------- q/k/v preparation
+// From the float32 rows of the fused projection [q: Hq*hd | k: Hkv*hd | v: Hkv*vd]: add the bias (if any), rotate the
+// first ``rot`` numbers of every q and k head (pair (i, i + rot/2), or (2i, 2i+1) with ``interleaved``; cosine and
+// sine times ``magnitude``), divide every q and k head by its root mean square (``norm_eps`` > 0; none otherwise),
+// all in float32; then write q to ``q_out`` [n, Hq*hd] and k and v into the cache page of the token's position.
+// One warp per head.
+namespace {
+constexpr int PREP_WARPS = 4;
+
+__device__ __forceinline__ void prep_sincos(int pos, const float* __restrict__ inv_freq, int half, int j, float* s,
+                                            float* c) {
+  const double f = (double)inv_freq[j] + (double)inv_freq[half + j];
+  double a = (double)pos * f;
+  a -= 6.283185307179586476925286766559 * rint(a * 0.15915494309189533576888376337251);
+  sincosf((float)a, s, c);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(PREP_WARPS * 32)
+qkv_prepare_kernel(const float* __restrict__ qkv, int Hq, int Hkv, int hd, int vd, const void* __restrict__ bias,
+                   int bias_dtype, const float* __restrict__ inv_freq, int rot, int interleaved, float magnitude,
+                   float norm_eps, const int* __restrict__ positions, const int* __restrict__ tok_entry,
+                   const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, T* __restrict__ q_out,
+                   T* __restrict__ cache, int page_size, int write_kv, long long n_pages) {
+  bspec::pdl_prologue(19);
+  __shared__ float xs[PREP_WARPS][MAX_HD];
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slot = blockIdx.y * PREP_WARPS + warp;            // q heads, then k heads, then v heads
+  if (slot >= Hq + 2 * Hkv) return;
+  const int pos = positions[t];
+  const int ld = (Hq + Hkv) * hd + Hkv * vd;
+  const bool is_v = slot >= Hq + Hkv;
+  const int width = is_v ? vd : hd;
+  const int col0 = is_v ? (Hq + Hkv) * hd + (slot - Hq - Hkv) * vd : slot * hd;
+  const float* src = qkv + (size_t)t * ld + col0;
+  float* x = xs[warp];
+  for (int d = lane; d < width; d += 32)
+    x[d] = src[d] + (bias != nullptr ? load_as_f32(bias, bias_dtype, (size_t)col0 + d) : 0.f);
+  __syncwarp();
+  float ss = 0.f;
+  if (!is_v) {
+    const int half = rot / 2;
+    for (int j = lane; j < half; j += 32) {
+      float sn, c;
+      prep_sincos(pos, inv_freq, half, j, &sn, &c);
+      sn *= magnitude;
+      c *= magnitude;
+      const int a = interleaved ? 2 * j : j, b = interleaved ? 2 * j + 1 : j + half;
+      const float u = x[a], v = x[b];
+      x[a] = u * c - v * sn;
+      x[b] = v * c + u * sn;
+    }
+    __syncwarp();
+    if (norm_eps > 0.f) {
+      for (int d = lane; d < hd; d += 32) ss += x[d] * x[d];
+      ss = warp_sum(ss);
+    }
+  }
+  const float r = (!is_v && norm_eps > 0.f) ? 1.f / sqrtf(ss / (float)hd + norm_eps) : 1.f;
+  T* dst = nullptr;
+  if (slot < Hq) {
+    dst = q_out + ((size_t)t * Hq + slot) * hd;
+  } else if (write_kv) {
+    const int e = tok_entry[t];
+    if (bspec::in_range(pos / page_size, kv_indptr[e + 1] - kv_indptr[e], 113)) {
+      const int page = kv_indices[kv_indptr[e] + pos / page_size];
+      if (bspec::in_range(page, n_pages, 114)) {
+        const size_t k_elems = (size_t)Hkv * page_size * hd;
+        const size_t page_elems = k_elems + (size_t)Hkv * page_size * vd;
+        const int row = pos % page_size;
+        dst = cache + (size_t)page * page_elems +
+              (is_v ? k_elems + ((size_t)(slot - Hq - Hkv) * page_size + row) * vd
+                    : ((size_t)(slot - Hq) * page_size + row) * hd);
+      }
+    }
+  }
+  if (dst != nullptr)
+    for (int d = lane; d < width; d += 32) dst[d] = from_f32<T>(x[d] * r);
+}
+}  // namespace
+
+BSPEC_API int bspec_qkv_prepare(const float* qkv, int n, int Hq, int Hkv, int hd, int vd, const void* bias,
+                                int bias_dtype, const float* inv_freq, int rot, int interleaved, float magnitude,
+                                float norm_eps, const int* positions, const int* tok_entry, const int* kv_indptr,
+                                const int* kv_indices, void* q_out, void* cache, int dtype, int page_size, int write_kv,
+                                long long n_pages, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (hd <= 0 || hd > MAX_HD || vd <= 0 || vd > MAX_HD || rot < 0 || rot > hd || rot % 2 != 0 ||
+      (rot > 0 && inv_freq == nullptr))
+    return (int)cudaErrorInvalidValue;
+  const dim3 grid(n, (Hq + 2 * Hkv + PREP_WARPS - 1) / PREP_WARPS);
+  if (grid.y > 65535) return (int)cudaErrorInvalidConfiguration;
+  if (dtype == BSPEC_F32)
+    BSPEC_LAUNCH((qkv_prepare_kernel<float>), grid, PREP_WARPS * 32, 0, stream, qkv, Hq, Hkv, hd, vd, bias, bias_dtype,
+                 inv_freq, rot, interleaved, magnitude, norm_eps, positions, tok_entry, kv_indptr, kv_indices,
+                 (float*)q_out, (float*)cache, page_size, write_kv, n_pages);
+  else
+    BSPEC_LAUNCH((qkv_prepare_kernel<__nv_bfloat16>), grid, PREP_WARPS * 32, 0, stream, qkv, Hq, Hkv, hd, vd, bias,
+                 bias_dtype, inv_freq, rot, interleaved, magnitude, norm_eps, positions, tok_entry, kv_indptr,
+                 kv_indices, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, page_size, write_kv, n_pages);
   return BSPEC_LAUNCH_CHECK();
 }
 

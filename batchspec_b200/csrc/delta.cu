@@ -1,0 +1,246 @@
+// Gated delta rule mixer: a recurrent layer whose per-request state is one [key dim x value dim] matrix per head
+// plus the last inputs of its short convolutions.  Per head and token, all in float32:
+//
+//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+//
+// Three kernels, one after the other on the stream:
+//   delta_prepare     per token: causal short convolution + silu of the q, k, v channels (the inputs before the
+//                     portion come from the request's state), unit length of every q and k head (q also times a
+//                     scale), beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias))
+//   delta_recurrence  per (request, head, 32 value columns): the token loop over the portion with the state in
+//                     registers (a column of S is spread over four lanes), state read at the start and written at
+//                     the end; one block per request also moves the convolutions' inputs on
+//   gated_rmsnorm     per (token, head): o / rms(o) * w * silu(gate)
+//
+// The order of every sum depends on the sizes alone, not on how a request was cut into portions or on what else is
+// in the step.
+#include "common.cuh"
+#include <math.h>
+using namespace bspec;
+
+namespace {
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 30.f ? x : log1pf(expf(x)); }
+
+// proj [n, ld] float32, columns [q: Gk*dim | k: Gk*dim | v: H*vdim | ... | b: H at b_off | a: H at a_off].
+// conv [C, taps] (C = 2*Gk*dim + H*vdim).  State row of a request: [H*vdim*dim matrix | (taps-1) x C inputs, oldest
+// first].  mix [n, C] and gates [n, 2H] (beta, then g) are float32.
+__global__ void __launch_bounds__(256)
+delta_prepare_kernel(const float* __restrict__ proj, int ld, int b_off, int a_off, const void* __restrict__ conv,
+                     const void* __restrict__ a_log, const void* __restrict__ dt_bias, int w_dtype,
+                     const float* __restrict__ state, long long state_stride, long long tail_off,
+                     const int* __restrict__ qo_indptr, const int* __restrict__ tok_entry,
+                     const int* __restrict__ state_slots, float* __restrict__ mix, float* __restrict__ gates, int H,
+                     int Gk, int dim, int vdim, int taps, float q_scale, float unit_eps) {
+  bspec::pdl_prologue(60);
+  extern __shared__ float ys[];                    // [C]
+  const int t = blockIdx.x;
+  const int e = tok_entry[t];
+  const int i = t - qo_indptr[e];                  // index of the token in its portion
+  const int C = 2 * Gk * dim + H * vdim;
+  const float* tail = state + (size_t)state_slots[e] * state_stride + tail_off;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float y = 0.f;
+    for (int j = taps - 1; j >= 0; --j) {          // oldest input first
+      const int rel = i - j;
+      const float x = rel >= 0 ? proj[(size_t)(t - j) * ld + c] : tail[(size_t)(rel + taps - 1) * C + c];
+      y += load_as_f32(conv, w_dtype, (size_t)c * taps + (taps - 1 - j)) * x;
+    }
+    ys[c] = silu_f(y);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  float* row = mix + (size_t)t * C;
+  for (int head = warp; head < 2 * Gk; head += nwarps) {        // q heads, then k heads
+    const float* y = ys + head * dim;
+    float ss = 0.f;
+    for (int d = lane; d < dim; d += 32) ss += y[d] * y[d];
+    ss = warp_sum(ss);
+    const float r = (head < Gk ? q_scale : 1.f) / sqrtf(ss + unit_eps);
+    for (int d = lane; d < dim; d += 32) row[head * dim + d] = y[d] * r;
+  }
+  for (int c = 2 * Gk * dim + threadIdx.x; c < C; c += blockDim.x) row[c] = ys[c];
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    const float b = proj[(size_t)t * ld + b_off + h], a = proj[(size_t)t * ld + a_off + h];
+    gates[(size_t)t * 2 * H + h] = 1.f / (1.f + expf(-b));
+    const float rate = expf(load_as_f32(a_log, w_dtype, h)) * softplus_f(a + load_as_f32(dt_bias, w_dtype, h));
+    gates[(size_t)t * 2 * H + H + h] = expf(-rate);
+  }
+}
+
+constexpr int COLS = 32;          // value columns of a block
+constexpr int LANES = 4;          // lanes that share one column of S
+constexpr int TILE = 8;           // tokens whose q, k, v, beta, g are staged in shared memory at a time
+constexpr int MAX_DIM = 256;
+
+// R: floats of a column that one lane holds (a multiple of 4, dim <= 4 R).  A lane holds rows 16 c + 4 r + {0..3}
+// for c < R / 4, so that the four lanes of a column read 64 contiguous bytes of state at a time.
+template <int R>
+__global__ void __launch_bounds__(COLS * LANES)
+delta_recurrence_kernel(const float* __restrict__ mix, const float* __restrict__ gates, const float* __restrict__ proj,
+                        int ld, float* __restrict__ state, long long state_stride, long long tail_off,
+                        const int* __restrict__ qo_indptr, const int* __restrict__ state_slots,
+                        float* __restrict__ out, int H, int Gk, int dim, int vdim, int taps) {
+  bspec::pdl_prologue(61);
+  __shared__ __align__(16) float qs[TILE][MAX_DIM];
+  __shared__ __align__(16) float ks[TILE][MAX_DIM];
+  __shared__ float vs[TILE][COLS];
+  __shared__ float bg[TILE][2];
+  const int e = blockIdx.z, h = blockIdx.y;
+  const int q_begin = qo_indptr[e], n = qo_indptr[e + 1] - q_begin;
+  const int C = 2 * Gk * dim + H * vdim;
+  float* srow = state + (size_t)state_slots[e] * state_stride;
+  if (n <= 0) return;
+  if (blockIdx.x == 0 && h == 0 && taps > 1) {
+    // the convolutions' inputs: slot s holds the input at index n + s - (taps - 1) of this portion, or what an
+    // older slot held; ascending s, so that a slot is read before it is overwritten
+    float* tail = srow + tail_off;
+    for (int c = threadIdx.x; c < C; c += blockDim.x)
+      for (int s = 0; s < taps - 1; ++s) {
+        const int rel = n + s - (taps - 1);
+        tail[(size_t)s * C + c] = rel >= 0 ? proj[(size_t)(q_begin + rel) * ld + c] : tail[(size_t)(s + n) * C + c];
+      }
+  }
+  const int col = threadIdx.x / LANES, r = threadIdx.x % LANES;
+  const int j = blockIdx.x * COLS + col;
+  const bool live = j < vdim;
+  const int kh = h / (H / Gk);
+  float s[R];
+  float* sp = srow + ((size_t)h * vdim + (live ? j : 0)) * dim;
+#pragma unroll
+  for (int c = 0; c < R / 4; ++c) {
+    const int row = 16 * c + 4 * r;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live && row < dim) v = *reinterpret_cast<const float4*>(sp + row);
+    s[4 * c] = v.x; s[4 * c + 1] = v.y; s[4 * c + 2] = v.z; s[4 * c + 3] = v.w;
+  }
+  for (int t0 = 0; t0 < n; t0 += TILE) {
+    const int nt = min(TILE, n - t0);
+    __syncthreads();
+    for (int w = threadIdx.x; w < nt * dim; w += blockDim.x) {
+      const int tt = w / dim, d = w - tt * dim;
+      const float* row = mix + (size_t)(q_begin + t0 + tt) * C;
+      qs[tt][d] = row[kh * dim + d];
+      ks[tt][d] = row[(Gk + kh) * dim + d];
+    }
+    for (int w = threadIdx.x; w < nt * COLS; w += blockDim.x) {
+      const int tt = w / COLS, cc = w - tt * COLS;
+      const int jj = blockIdx.x * COLS + cc;
+      vs[tt][cc] = jj < vdim ? mix[(size_t)(q_begin + t0 + tt) * C + 2 * Gk * dim + h * vdim + jj] : 0.f;
+    }
+    if (threadIdx.x < nt * 2) {
+      const int tt = threadIdx.x >> 1, which = threadIdx.x & 1;
+      bg[tt][which] = gates[(size_t)(q_begin + t0 + tt) * 2 * H + which * H + h];
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float beta = bg[tt][0], g = bg[tt][1];
+      float dk = 0.f;
+#pragma unroll
+      for (int c = 0; c < R / 4; ++c) {
+        const int row = 16 * c + 4 * r;
+        if (row < dim) {
+          const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][row]);
+          s[4 * c] *= g; s[4 * c + 1] *= g; s[4 * c + 2] *= g; s[4 * c + 3] *= g;
+          dk += s[4 * c] * k4.x; dk += s[4 * c + 1] * k4.y; dk += s[4 * c + 2] * k4.z; dk += s[4 * c + 3] * k4.w;
+        }
+      }
+      dk += __shfl_xor_sync(0xffffffffu, dk, 1);
+      dk += __shfl_xor_sync(0xffffffffu, dk, 2);
+      const float u = beta * (vs[tt][col] - dk);
+      float dq = 0.f;
+#pragma unroll
+      for (int c = 0; c < R / 4; ++c) {
+        const int row = 16 * c + 4 * r;
+        if (row < dim) {
+          const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][row]);
+          const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][row]);
+          s[4 * c] += k4.x * u; s[4 * c + 1] += k4.y * u; s[4 * c + 2] += k4.z * u; s[4 * c + 3] += k4.w * u;
+          dq += s[4 * c] * q4.x; dq += s[4 * c + 1] * q4.y; dq += s[4 * c + 2] * q4.z; dq += s[4 * c + 3] * q4.w;
+        }
+      }
+      dq += __shfl_xor_sync(0xffffffffu, dq, 1);
+      dq += __shfl_xor_sync(0xffffffffu, dq, 2);
+      if (live && r == 0) out[(size_t)(q_begin + t0 + tt) * H * vdim + h * vdim + j] = dq;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int c = 0; c < R / 4; ++c) {
+      const int row = 16 * c + 4 * r;
+      if (row < dim) *reinterpret_cast<float4*>(sp + row) = make_float4(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3]);
+    }
+  }
+}
+
+// out[t, h*V + j] = o[t, h, j] / sqrt(mean_j o^2 + eps) * w[j] * silu(gate[t, h*V + j]); one warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(128)
+gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ gate, long long gate_stride,
+                     const void* __restrict__ w, int w_dtype, T* __restrict__ out, int n, int H, int V, float eps) {
+  bspec::pdl_prologue(62);
+  const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (item >= n * H) return;
+  const int t = item / H, h = item - t * H;
+  const float* x = o + ((size_t)t * H + h) * V;
+  float ss = 0.f;
+  for (int j = lane; j < V; j += 32) ss += x[j] * x[j];
+  ss = warp_sum(ss);
+  const float r = 1.f / sqrtf(ss / (float)V + eps);
+  const float* gp = gate + (size_t)t * gate_stride + (size_t)h * V;
+  T* op = out + ((size_t)t * H + h) * V;
+  for (int j = lane; j < V; j += 32) op[j] = from_f32<T>(x[j] * r * load_as_f32(w, w_dtype, j) * silu_f(gp[j]));
+}
+}  // namespace
+
+BSPEC_API int bspec_delta_prepare(const float* proj, int n, int ld, int b_off, int a_off, const void* conv,
+                                  const void* a_log, const void* dt_bias, int w_dtype, const float* state,
+                                  long long state_stride, long long tail_off, const int* qo_indptr,
+                                  const int* tok_entry, const int* state_slots, float* mix, float* gates, int H, int Gk,
+                                  int dim, int vdim, int taps, float q_scale, float unit_eps, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (H <= 0 || Gk <= 0 || H % Gk != 0 || taps < 1) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)(2 * Gk * dim + H * vdim) * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  static bool raised[bspec::kMaxDevices] = {};
+  if (smem > 48 * 1024 && !raised[bspec::current_device()]) {
+    cudaError_t e = cudaFuncSetAttribute(delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    raised[bspec::current_device()] = true;
+  }
+  BSPEC_LAUNCH(delta_prepare_kernel, n, 256, smem, stream, proj, ld, b_off, a_off, conv, a_log, dt_bias, w_dtype, state,
+               state_stride, tail_off, qo_indptr, tok_entry, state_slots, mix, gates, H, Gk, dim, vdim, taps, q_scale,
+               unit_eps);
+  return BSPEC_LAUNCH_CHECK();
+}
+
+BSPEC_API int bspec_delta_recurrence(const float* mix, const float* gates, const float* proj, int ld, float* state,
+                                     long long state_stride, long long tail_off, const int* qo_indptr,
+                                     const int* state_slots, float* out, int n_entries, int H, int Gk, int dim,
+                                     int vdim, int taps, cudaStream_t stream) {
+  if (n_entries <= 0) return 0;
+  if (dim <= 0 || dim > MAX_DIM || dim % 4 != 0 || H % Gk != 0 || n_entries > 65535 || H > 65535)
+    return (int)cudaErrorInvalidValue;
+  const dim3 grid((vdim + COLS - 1) / COLS, H, n_entries);
+#define LR(R) BSPEC_LAUNCH((delta_recurrence_kernel<R>), grid, COLS * LANES, 0, stream, mix, gates, proj, ld, state, \
+                           state_stride, tail_off, qo_indptr, state_slots, out, H, Gk, dim, vdim, taps)
+  if (dim <= 32) LR(8); else if (dim <= 64) LR(16); else if (dim <= 128) LR(32); else LR(64);
+#undef LR
+  return BSPEC_LAUNCH_CHECK();
+}
+
+BSPEC_API int bspec_gated_rmsnorm(const float* o, const float* gate, long long gate_stride, const void* w, int w_dtype,
+                                  void* out, int out_dtype, int n, int H, int V, float eps, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int blocks = (n * H + 3) / 4;
+  if (out_dtype == BSPEC_F32)
+    BSPEC_LAUNCH((gated_rmsnorm_kernel<float>), blocks, 128, 0, stream, o, gate, gate_stride, w, w_dtype, (float*)out, n, H, V, eps);
+  else
+    BSPEC_LAUNCH((gated_rmsnorm_kernel<__nv_bfloat16>), blocks, 128, 0, stream, o, gate, gate_stride, w, w_dtype,
+                 (__nv_bfloat16*)out, n, H, V, eps);
+  return BSPEC_LAUNCH_CHECK();
+}
+
+BSPEC_DEFINE_TRACE_SETTER(bspec_trace_set_delta)
+BSPEC_DEFINE_BOUNDS_REPORT(bspec_bounds_report_delta)

@@ -62,7 +62,8 @@ template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16*
 
 template <typename TD, typename TO, typename TW, int VPT>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
-                                       const TW* __restrict__ weight, TO* __restrict__ out, int d, float eps) {
+                                       const TW* __restrict__ weight, TO* __restrict__ out, int d, float eps,
+                                       float delta_scale, int exact) {
   bspec::pdl_prologue(2);
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * d;
@@ -77,14 +78,15 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
         float dl[4];
         load4<TD>(delta + base + i, dl);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) x[k][j] += dl[j];
+        for (int j = 0; j < 4; ++j) x[k][j] += delta_scale * dl[j];
         store4<float>(resid + base + i, x[k]);
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) ss += x[k][j] * x[k][j];
     }
   }
-  const float r = rsqrtf(block_sum(ss, scratch) / (float)d + eps);
+  const float ms = block_sum(ss, scratch) / (float)d + eps;
+  const float r = exact ? 1.f / sqrtf(ms) : rsqrtf(ms);
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
     const int i = 4 * (threadIdx.x + k * blockDim.x);
@@ -92,7 +94,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
       float w[4], y[4];
       load4<TW>(weight + i, w);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) y[j] = to_f32(from_f32<TO>(to_f32(from_f32<TO>(x[k][j] * r)) * w[j]));
+      for (int j = 0; j < 4; ++j)
+        y[j] = exact ? x[k][j] * r * w[j] : to_f32(from_f32<TO>(to_f32(from_f32<TO>(x[k][j] * r)) * w[j]));
       store4<TO>(out + base + i, y);
     }
   }
@@ -101,7 +104,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
 template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    const void* __restrict__ weight, int w_dtype, TO* __restrict__ out, int d,
-                                   float eps) {
+                                   float eps, float delta_scale, int exact) {
   bspec::pdl_prologue(2);
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * d;
@@ -109,23 +112,23 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float v = resid[base + i];
     if (delta != nullptr) {
-      v += to_f32(delta[base + i]);
+      v += delta_scale * to_f32(delta[base + i]);
       resid[base + i] = v;
     }
     ss += v * v;
   }
   const float total = block_sum(ss, scratch);
-  const float r = rsqrtf(total / (float)d + eps);
+  const float r = exact ? 1.f / sqrtf(total / (float)d + eps) : rsqrtf(total / (float)d + eps);
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     const float n = resid[base + i] * r;
     const float w = load_as_f32(weight, w_dtype, i);
-    out[base + i] = from_f32<TO>(to_f32(from_f32<TO>(n)) * w);
+    out[base + i] = exact ? from_f32<TO>(n * w) : from_f32<TO>(to_f32(from_f32<TO>(n)) * w);
   }
 }
 
 template <typename TD, typename TO, typename TW>
 static void launch_add_rmsnorm_vec(float* resid, const void* delta, const void* weight, void* out, int n, int d,
-                                   float eps, cudaStream_t stream) {
+                                   float eps, float delta_scale, int exact, cudaStream_t stream) {
   const int quads = d / 4;
   int threads = quads >= 1024 ? 1024 : ((quads + 31) / 32) * 32;
   // Many rows (a prompt): four quads per thread, so that a thread has more loads in flight and several rows share
@@ -134,27 +137,30 @@ static void launch_add_rmsnorm_vec(float* resid, const void* delta, const void* 
   if (sizeof(TO) == 2 && n >= 512 && quads >= 128) threads = (((quads + 3) / 4 + 31) / 32) * 32;
   if (threads < 32) threads = 32;
   const int vpt = (quads + threads - 1) / threads;
-#define LV(V) BSPEC_LAUNCH((add_rmsnorm_vec_kernel<TD, TO, TW, V>), n, threads, 0, stream, resid, (const TD*)delta, (const TW*)weight, (TO*)out, d, eps)
+#define LV(V) BSPEC_LAUNCH((add_rmsnorm_vec_kernel<TD, TO, TW, V>), n, threads, 0, stream, resid, (const TD*)delta, (const TW*)weight, (TO*)out, d, eps, delta_scale, exact)
   if (vpt <= 1) LV(1); else if (vpt <= 2) LV(2); else LV(4);
 #undef LV
 }
 
+// delta_scale multiplies delta in the sum.  exact != 0: one rounding, resid / sqrt(mean + eps) * w in float32 and
+// then the cast; 0: the cast to the output type comes before the product with w, which is taken in that type.
 BSPEC_API int bspec_add_rmsnorm(float* resid, const void* delta, int delta_dtype, const void* weight, int w_dtype,
-                                void* out, int out_dtype, int n, int d, float eps, cudaStream_t stream) {
+                                void* out, int out_dtype, int n, int d, float eps, float delta_scale, int exact,
+                                cudaStream_t stream) {
   if (n <= 0) return 0;
   const bool same = delta_dtype == out_dtype;
   if (same && d % 4 == 0 && d <= 4 * 4 * 1024) {
     if (out_dtype == BSPEC_F32) {
-      if (w_dtype == BSPEC_F32) launch_add_rmsnorm_vec<float, float, float>(resid, delta, weight, out, n, d, eps, stream);
-      else launch_add_rmsnorm_vec<float, float, __nv_bfloat16>(resid, delta, weight, out, n, d, eps, stream);
+      if (w_dtype == BSPEC_F32) launch_add_rmsnorm_vec<float, float, float>(resid, delta, weight, out, n, d, eps, delta_scale, exact, stream);
+      else launch_add_rmsnorm_vec<float, float, __nv_bfloat16>(resid, delta, weight, out, n, d, eps, delta_scale, exact, stream);
     } else {
-      if (w_dtype == BSPEC_F32) launch_add_rmsnorm_vec<__nv_bfloat16, __nv_bfloat16, float>(resid, delta, weight, out, n, d, eps, stream);
-      else launch_add_rmsnorm_vec<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(resid, delta, weight, out, n, d, eps, stream);
+      if (w_dtype == BSPEC_F32) launch_add_rmsnorm_vec<__nv_bfloat16, __nv_bfloat16, float>(resid, delta, weight, out, n, d, eps, delta_scale, exact, stream);
+      else launch_add_rmsnorm_vec<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(resid, delta, weight, out, n, d, eps, delta_scale, exact, stream);
     }
     return BSPEC_LAUNCH_CHECK();
   }
   const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
-#define L(TD, TO) BSPEC_LAUNCH((add_rmsnorm_kernel<TD, TO>), n, threads, 0, stream, resid, (const TD*)delta, weight, w_dtype, (TO*)out, d, eps)
+#define L(TD, TO) BSPEC_LAUNCH((add_rmsnorm_kernel<TD, TO>), n, threads, 0, stream, resid, (const TD*)delta, weight, w_dtype, (TO*)out, d, eps, delta_scale, exact)
   if (delta_dtype == BSPEC_F32 && out_dtype == BSPEC_F32) L(float, float);
   else if (delta_dtype == BSPEC_BF16 && out_dtype == BSPEC_BF16) L(__nv_bfloat16, __nv_bfloat16);
   else if (delta_dtype == BSPEC_F32 && out_dtype == BSPEC_BF16) L(float, __nv_bfloat16);
@@ -276,24 +282,51 @@ BSPEC_API int bspec_add_layernorm(float* resid, const void* delta, int delta_dty
 // ---------------------------------------------------------------- row gather (+ pending add)
 template <typename TD>
 __global__ void gather_rows_add_kernel(const float* __restrict__ resid, const TD* __restrict__ pending,
-                                       const int* __restrict__ rows, float* __restrict__ out, int d, int n_src) {
+                                       const int* __restrict__ rows, float* __restrict__ out, int d, int n_src,
+                                       float scale) {
   bspec::pdl_prologue(3);
   if (!bspec::in_range(rows[blockIdx.x], n_src, 102)) return;
   const size_t src = (size_t)rows[blockIdx.x] * d, dst = (size_t)blockIdx.x * d;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float v = resid[src + i];
-    if (pending != nullptr) v += to_f32(pending[src + i]);
+    if (pending != nullptr) v += scale * to_f32(pending[src + i]);
     out[dst + i] = v;
   }
 }
 
 BSPEC_API int bspec_gather_rows_add(const float* resid, const void* pending, int pending_dtype, const int* rows,
-                                    float* out, int n_out, int d, int n_src, cudaStream_t stream) {
+                                    float* out, int n_out, int d, int n_src, float scale, cudaStream_t stream) {
   if (n_out <= 0) return 0;
   if (pending_dtype == BSPEC_F32)
-    BSPEC_LAUNCH((gather_rows_add_kernel<float>), n_out, 256, 0, stream, resid, (const float*)pending, rows, out, d, n_src);
+    BSPEC_LAUNCH((gather_rows_add_kernel<float>), n_out, 256, 0, stream, resid, (const float*)pending, rows, out, d, n_src, scale);
   else
-    BSPEC_LAUNCH((gather_rows_add_kernel<__nv_bfloat16>), n_out, 256, 0, stream, resid, (const __nv_bfloat16*)pending, rows, out, d, n_src);
+    BSPEC_LAUNCH((gather_rows_add_kernel<__nv_bfloat16>), n_out, 256, 0, stream, resid, (const __nv_bfloat16*)pending, rows, out, d, n_src, scale);
+  return BSPEC_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- residual update
+// resid += scale * pending (if pending) + extra (if extra), float32, in this order.
+template <typename TD>
+__global__ void residual_update_kernel(float* __restrict__ resid, const TD* __restrict__ pending, float scale,
+                                       const float* __restrict__ extra, size_t total) {
+  bspec::pdl_prologue(18);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    float v = resid[i];
+    if (pending != nullptr) v += scale * to_f32(pending[i]);
+    if (extra != nullptr) v += extra[i];
+    resid[i] = v;
+  }
+}
+
+BSPEC_API int bspec_residual_update(float* resid, const void* pending, int pending_dtype, float scale,
+                                    const float* extra, long long total, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  const size_t want = ((size_t)total + 255) / 256, cap = (size_t)bspec::sm_count() * 16;
+  const int blocks = (int)(want > cap ? cap : want);
+  if (pending_dtype == BSPEC_F32)
+    BSPEC_LAUNCH((residual_update_kernel<float>), blocks, 256, 0, stream, resid, (const float*)pending, scale, extra, (size_t)total);
+  else
+    BSPEC_LAUNCH((residual_update_kernel<__nv_bfloat16>), blocks, 256, 0, stream, resid, (const __nv_bfloat16*)pending, scale, extra, (size_t)total);
   return BSPEC_LAUNCH_CHECK();
 }
 
@@ -306,15 +339,16 @@ __device__ __forceinline__ size_t gate_col(size_t col, int inter, int group) {
 __device__ __forceinline__ size_t up_col(size_t col, int inter, int group) {
   return group > 0 ? (col / group) * 2 * group + group + (col % group) : inter + col;
 }
+// act 0: silu(gate) * up;  act 1: relu(gate) * up
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ u, T* __restrict__ m, int inter, size_t total, int group) {
+__global__ void silu_mul_kernel(const T* __restrict__ u, T* __restrict__ m, int inter, size_t total, int group, int act) {
   bspec::pdl_prologue(4);
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t row = idx / inter, col = idx - row * inter;
     const float g = to_f32(u[row * 2 * inter + gate_col(col, inter, group)]);
     const float up = to_f32(u[row * 2 * inter + up_col(col, inter, group)]);
-    const float s = g / (1.f + expf(-g));
+    const float s = act == 1 ? fmaxf(g, 0.f) : g / (1.f + expf(-g));
     m[idx] = from_f32<T>(s * up);
   }
 }
@@ -323,7 +357,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ u, T* __restrict__ m, int 
 // over the rows (no 64-bit divisions per element), the exponential and the quotient in their fast forms (their
 // error is far below bfloat16's step)
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ u, __nv_bfloat16* __restrict__ m, int inter,
-                                       int n, int group) {
+                                       int n, int group, int act) {
   bspec::pdl_prologue(4);
   const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
   if (c8 * 8 >= inter) return;
@@ -341,14 +375,15 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ u, __nv
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float ga = __low2float(g2[j]), gb = __high2float(g2[j]);
-      const float sa = __fdividef(ga, 1.f + __expf(-ga)), sb = __fdividef(gb, 1.f + __expf(-gb));
+      const float sa = act == 1 ? fmaxf(ga, 0.f) : __fdividef(ga, 1.f + __expf(-ga));
+      const float sb = act == 1 ? fmaxf(gb, 0.f) : __fdividef(gb, 1.f + __expf(-gb));
       o2[j] = __floats2bfloat162_rn(sa * __low2float(u2[j]), sb * __high2float(u2[j]));
     }
     *reinterpret_cast<uint4*>(m + (size_t)row * inter + col) = ov;
   }
 }
 
-BSPEC_API int bspec_silu_mul(const void* u, void* m, int dtype, int n, int inter, int group, cudaStream_t stream) {
+static int launch_gated_mul(const void* u, void* m, int dtype, int n, int inter, int group, int act, cudaStream_t stream) {
   const size_t total = (size_t)n * inter;
   if (total == 0) return 0;
   const int threads = 256;
@@ -358,18 +393,27 @@ BSPEC_API int bspec_silu_mul(const void* u, void* m, int dtype, int n, int inter
     const int tx = inter8 >= 256 ? 256 : ((inter8 + 31) / 32) * 32;
     const dim3 grid((inter8 + tx - 1) / tx, n > 32768 ? 32768 : n);
     BSPEC_LAUNCH((silu_mul_bf16x8_kernel), grid, tx, 0, stream, (const __nv_bfloat16*)u, (__nv_bfloat16*)m, inter, n,
-                 group);
+                 group, act);
     return BSPEC_LAUNCH_CHECK();
   }
   size_t want = (total + threads - 1) / threads;
   const size_t cap = (size_t)bspec::sm_count() * 32;
   const int blocks = (int)(want > cap ? cap : want);
   if (dtype == BSPEC_F32)
-    BSPEC_LAUNCH((silu_mul_kernel<float>), blocks, threads, 0, stream, (const float*)u, (float*)m, inter, total, group);
+    BSPEC_LAUNCH((silu_mul_kernel<float>), blocks, threads, 0, stream, (const float*)u, (float*)m, inter, total, group, act);
   else
     BSPEC_LAUNCH((silu_mul_kernel<__nv_bfloat16>), blocks, threads, 0, stream, (const __nv_bfloat16*)u,
-                 (__nv_bfloat16*)m, inter, total, group);
+                 (__nv_bfloat16*)m, inter, total, group, act);
   return BSPEC_LAUNCH_CHECK();
+}
+
+BSPEC_API int bspec_silu_mul(const void* u, void* m, int dtype, int n, int inter, int group, cudaStream_t stream) {
+  return launch_gated_mul(u, m, dtype, n, inter, group, 0, stream);
+}
+
+// relu(gate) * up, the layouts of silu_mul
+BSPEC_API int bspec_relu_mul(const void* u, void* m, int dtype, int n, int inter, int group, cudaStream_t stream) {
+  return launch_gated_mul(u, m, dtype, n, inter, group, 1, stream);
 }
 
 // ---------------------------------------------------------------- clamped GLU:  g sigmoid(alpha g) (u + 1)

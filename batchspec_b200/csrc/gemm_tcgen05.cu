@@ -46,7 +46,8 @@ struct GemmParams {
   int kblocks_per_split;
   int stages;
   int glu;               // rows of W come in groups of 16 = 8 gate rows + their 8 up rows; C[M, N/2] = act(gate, up):
-                         // 1: silu(gate) * up;  2: g sigmoid(alpha g) (u + 1), g = min(gate, limit), u = clamp(up, +-limit)
+                         // 1: silu(gate) * up;  2: g sigmoid(alpha g) (u + 1), g = min(gate, limit), u = clamp(up, +-limit);
+                         // 3: relu(gate) * up
   float glu_alpha, glu_limit;
   int prefetch_kb;       // K blocks of weights (beyond the stages) to pull into the L2 before waiting on the predecessor
   // fused q/k/v projection (rope_freq != nullptr): tile t of W is head t (q heads, then k heads, then v heads)
@@ -80,6 +81,7 @@ __device__ __forceinline__ float glu_combine(int kind, float alpha, float limit,
     u = fminf(fmaxf(u, -limit), limit);
     return g / (1.f + expf(-alpha * g)) * (u + 1.f);
   }
+  if (kind == 3) return fmaxf(g, 0.f) * u;
   return g / (1.f + expf(-g)) * u;
 }
 
@@ -443,7 +445,7 @@ static int launch_gemm(const void* X, const void* W, void* C, int M, int N, int 
   if (glu && (N % 16 != 0)) return (int)cudaErrorInvalidValue;
   GemmParams p;
   p.C = C; p.status = status;
-  p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.glu = glu == 2 ? 2 : (glu ? 1 : 0);
+  p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.glu = glu == 2 ? 2 : (glu == 3 ? 3 : (glu ? 1 : 0));
   p.glu_alpha = glu_alpha; p.glu_limit = glu_limit;
   p.swap = plan[0]; p.bn = plan[1]; p.splits = plan[2]; p.stages = plan[3];
   p.rope_freq = nullptr; p.positions = p.tok_entry = p.kv_indptr = p.kv_indices = nullptr; p.cache = nullptr;
@@ -508,7 +510,7 @@ static int launch_gemm(const void* X, const void* W, void* C, int M, int N, int 
 
 // C = X W^T.  `status`: one int on the device, 0 unless a bounded wait ran out.
 // glu != 0: the rows of W come in groups of 16 (8 gate rows, then the 8 matching up rows; N a multiple of 16) and
-// C is [M, N/2] = silu(gate) * up.
+// C is [M, N/2] = silu(gate) * up (glu 1) or relu(gate) * up (glu 3).
 BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N, int K, int out_f32, int glu,
                             int* status, int sm_count, cudaStream_t stream) {
   return launch_gemm(X, W, C, M, N, K, out_f32, glu, status, sm_count, nullptr, stream);

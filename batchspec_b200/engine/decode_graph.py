@@ -151,7 +151,7 @@ class DecodeGraph:
                     m[base + lo:base + len(table)] = table[lo:]
                     self.row_pages[i][g] = len(table)
                     self.tables_dirty = True
-                elif cache.groups[g].spec.policy == "window":
+                elif cache.groups[g].spec.policy in ("window", "chunk"):
                     base = off[f"kv_indices{g}"] + i * P         # released pages turn into -1 in place
                     m[base:base + len(table)] = table
                     self.tables_dirty = True

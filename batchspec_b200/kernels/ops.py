@@ -40,9 +40,25 @@ def _dtype_code(t: torch.dtype) -> int:
 
 _SIGNATURES = {
     "bspec_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
-    "bspec_add_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
-    "bspec_gather_rows_add": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "bspec_add_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float,
+                          c_int, c_void_p],
+    "bspec_gather_rows_add": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+    "bspec_residual_update": [c_void_p, c_void_p, c_int, c_float, c_void_p, c_longlong, c_void_p],
     "bspec_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "bspec_relu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "bspec_qkv_prepare": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float,
+                          c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                          c_longlong, c_void_p],
+    "bspec_attention_masked": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+                               c_longlong, c_void_p],
+    "bspec_delta_prepare": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                            c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                            c_int, c_int, c_int, c_float, c_float, c_void_p],
+    "bspec_delta_recurrence": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_void_p,
+                               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "bspec_gated_rmsnorm": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                            c_float, c_void_p],
     "bspec_rope_kv_append": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p],
     "bspec_rope_inplace": [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_float,
@@ -140,11 +156,12 @@ def set_pdl(on: bool) -> None:
 
 _TRACE_SETTERS = ["bspec_trace_set_attention_tcgen05", "bspec_trace_set_elementwise", "bspec_trace_set_attention_generic", "bspec_trace_set_attention_bf16",
                   "bspec_trace_set_gemm_fp32", "bspec_trace_set_sampling", "bspec_trace_set_gemm_tcgen05", "bspec_trace_set_latent",
-                  "bspec_trace_set_moe", "bspec_trace_set_latent_mma"]
+                  "bspec_trace_set_moe", "bspec_trace_set_latent_mma", "bspec_trace_set_delta"]
 TRACE_KERNEL_NAMES = {1: "embed", 2: "add_rmsnorm", 3: "gather_rows_add", 4: "silu_mul", 5: "rope_kv_append",
                       6: "rope_inplace", 7: "attn_generic", 8: "attn_decode", 9: "attn_prefill", 10: "sgemm",
                       11: "sample_threshold", 12: "sample_pick", 13: "sample_final", 14: "add_layernorm", 15: "clamped_glu",
-                      16: "gelu_erf", 17: "tanh_softcap", 20: "gemm_tcgen05", 30: "attn_prefill_tc", 40: "latent_prepare",
+                      16: "gelu_erf", 17: "tanh_softcap", 18: "residual_update", 19: "qkv_prepare", 60: "delta_prepare",
+                      61: "delta_recurrence", 62: "gated_rmsnorm", 20: "gemm_tcgen05", 30: "attn_prefill_tc", 40: "latent_prepare",
                       41: "latent_attn_generic", 42: "gate_heads", 43: "latent_attn_mma", 44: "latent_attn_join",
                       50: "moe_route", 51: "moe_plan", 52: "moe_grouped", 53: "moe_gather", 54: "moe_combine", 55: "moe_skinny", 56: "moe_skinny_mma", 57: "moe_rank", 58: "moe_offsets", 59: "moe_place"}
 
@@ -220,7 +237,10 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: floa
 
 
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
-                out: torch.Tensor) -> None:
+                out: torch.Tensor, delta_scale: float = 1.0, exact: bool = False) -> None:
+    """resid += delta_scale * delta (if given); out = the RMS-normalised rows times ``weight``.  ``exact``: the
+    product with the weight is taken in float32 and the result rounded once; otherwise the normalised row is cast
+    to the output type first and multiplied there."""
     _require_cuda(resid, delta, weight, out)
     assert resid.dtype == torch.float32 and resid.is_contiguous() and out.is_contiguous()
     n, d = resid.shape
@@ -230,18 +250,33 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
     dd = _dtype_code(delta.dtype) if delta is not None else _dtype_code(out.dtype)
     _check(load_library().bspec_add_rmsnorm(resid.data_ptr(), _ptr(delta), dd, weight.data_ptr(),
                                             _dtype_code(weight.dtype), out.data_ptr(), _dtype_code(out.dtype),
-                                            n, d, float(eps), _stream()), "add_rmsnorm")
+                                            n, d, float(eps), float(delta_scale), int(bool(exact)), _stream()),
+           "add_rmsnorm")
 
 
 def gather_rows_add(resid: torch.Tensor, pending: Optional[torch.Tensor], rows: torch.Tensor,
-                    out: torch.Tensor) -> None:
+                    out: torch.Tensor, scale: float = 1.0) -> None:
     _require_cuda(resid, pending, rows, out)
     assert resid.dtype == torch.float32 and out.dtype == torch.float32 and rows.dtype == torch.int32
     assert resid.is_contiguous() and out.is_contiguous() and (pending is None or pending.is_contiguous())
     pd = _dtype_code(pending.dtype) if pending is not None else F32
     _check(load_library().bspec_gather_rows_add(resid.data_ptr(), _ptr(pending), pd, rows.data_ptr(), out.data_ptr(),
-                                                out.shape[0], out.shape[1], resid.shape[0], _stream()),
+                                                out.shape[0], out.shape[1], resid.shape[0], float(scale), _stream()),
            "gather_rows_add")
+
+
+def residual_update(resid: torch.Tensor, pending: Optional[torch.Tensor], scale: float = 1.0,
+                    extra: Optional[torch.Tensor] = None) -> None:
+    """In place on the float32 residual: resid += scale * pending (if given) + extra (if given, float32)."""
+    _require_cuda(resid, pending, extra)
+    assert resid.dtype == torch.float32 and resid.is_contiguous()
+    assert pending is None or (pending.shape == resid.shape and pending.is_contiguous())
+    assert extra is None or (extra.shape == resid.shape and extra.is_contiguous() and extra.dtype == torch.float32)
+    if pending is None and extra is None:
+        return
+    _check(load_library().bspec_residual_update(resid.data_ptr(), _ptr(pending),
+                                                _dtype_code(pending.dtype) if pending is not None else F32,
+                                                float(scale), _ptr(extra), resid.numel(), _stream()), "residual_update")
 
 
 def add_layernorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, bias: torch.Tensor,
@@ -298,6 +333,15 @@ def silu_mul(u: torch.Tensor, out: torch.Tensor, group: int = 0) -> None:
                                          _stream()), "silu_mul")
 
 
+def relu_mul(u: torch.Tensor, out: torch.Tensor, group: int = 0) -> None:
+    """out = relu(gate) * up; the column layouts of ``silu_mul``."""
+    _require_cuda(u, out)
+    n, inter = out.shape
+    assert u.shape == (n, 2 * inter) and u.dtype == out.dtype and u.is_contiguous() and out.is_contiguous()
+    _check(load_library().bspec_relu_mul(u.data_ptr(), out.data_ptr(), _dtype_code(u.dtype), n, inter, int(group),
+                                         _stream()), "relu_mul")
+
+
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int = GLU_GROUP) -> torch.Tensor:
     """[I, d] gate and up rows -> [2I, d] in blocks of ``group`` gate rows followed by their up rows."""
     inter, d = gate.shape
@@ -305,9 +349,11 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int = GLU_GR
     return torch.stack([gate.view(inter // group, group, d), up.view(inter // group, group, d)], dim=1).reshape(2 * inter, d).contiguous()
 
 
-def linear_glu(x: torch.Tensor, w13: torch.Tensor, group: int = GLU_GROUP) -> torch.Tensor:
-    """silu(x Wg^T) * (x Wu^T) for bfloat16 with ``w13`` interleaved by ``interleave_gate_up``: one kernel with the
-    activation in the GEMM's epilogue for decode-sized steps, vendor GEMM + activation kernel otherwise."""
+def linear_glu(x: torch.Tensor, w13: torch.Tensor, group: int = GLU_GROUP, activation: str = "silu") -> torch.Tensor:
+    """act(x Wg^T) * (x Wu^T), act = silu or relu, for bfloat16 with ``w13`` interleaved by ``interleave_gate_up``:
+    one kernel with the activation in the GEMM's epilogue for decode-sized steps, vendor GEMM + activation kernel
+    otherwise."""
+    assert activation in ("silu", "relu")
     _require_cuda(x, w13)
     M, K = x.shape
     N = w13.shape[0]
@@ -315,12 +361,13 @@ def linear_glu(x: torch.Tensor, w13: torch.Tensor, group: int = GLU_GROUP) -> to
     if (GLU_FUSION and x.dtype == torch.bfloat16 and K % 8 == 0 and M > 0 and group == GLU_GROUP
             and x.is_contiguous() and (TC_GEMM == "all" or (TC_GEMM == "auto" and M <= TC_GEMM_MAX_M))):
         out = torch.empty((M, inter), dtype=x.dtype, device=x.device)
-        _check(load_library().bspec_gemm_tc(x.data_ptr(), w13.data_ptr(), out.data_ptr(), M, N, K, 0, 1,
+        _check(load_library().bspec_gemm_tc(x.data_ptr(), w13.data_ptr(), out.data_ptr(), M, N, K, 0,
+                                            3 if activation == "relu" else 1,
                                             _status_word(x.device).data_ptr(), sm_count(x.device), _stream()), "gemm_tc_glu")
         return out
     u = linear(x, w13)
     out = torch.empty((M, inter), dtype=x.dtype, device=x.device)
-    silu_mul(u, out, group)
+    (relu_mul if activation == "relu" else silu_mul)(u, out, group)
     return out
 
 
@@ -535,6 +582,109 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
         cache.shape[0], _stream()), "attention_generic")
 
 
+def qkv_prepare(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, v_dim: int,
+                bias: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], rotary_dim: int, interleaved: bool,
+                magnitude: float, norm_eps: float, positions: torch.Tensor, tok_entry: torch.Tensor,
+                kv_indptr: torch.Tensor, kv_indices: torch.Tensor, cache: torch.Tensor, page_size: int,
+                write_kv: bool = True) -> torch.Tensor:
+    """From the float32 rows [q | k | v] of the fused projection: bias, rotation of the first ``rotary_dim`` numbers
+    of every q and k head (cosine and sine times ``magnitude``), division of every q and k head by its root mean
+    square (``norm_eps`` > 0), in float32; returns q [n, n_heads * head_dim] in the cache's dtype and writes k and v
+    into the cache page of each token's position.  Page layout: [k: kv head, row, head_dim | v: kv head, row, v_dim]."""
+    _require_cuda(qkv, cache, positions)
+    n = qkv.shape[0]
+    assert qkv.dtype == torch.float32 and qkv.is_contiguous() and cache.is_contiguous()
+    assert qkv.shape[1] == (n_heads + n_kv_heads) * head_dim + n_kv_heads * v_dim
+    assert positions.dtype == torch.int32 and tok_entry.dtype == torch.int32
+    if bias is not None:
+        assert bias.numel() == qkv.shape[1] and bias.is_contiguous()
+    if rotary_dim:
+        assert inv_freq.dtype == torch.float32 and inv_freq.shape == (2, rotary_dim // 2) and inv_freq.is_contiguous()
+    q = torch.empty((n, n_heads * head_dim), dtype=cache.dtype, device=qkv.device)
+    _check(load_library().bspec_qkv_prepare(
+        qkv.data_ptr(), n, n_heads, n_kv_heads, head_dim, v_dim, _ptr(bias),
+        _dtype_code(bias.dtype) if bias is not None else F32, _ptr(inv_freq), int(rotary_dim), int(bool(interleaved)),
+        float(magnitude), float(norm_eps), positions.data_ptr(), tok_entry.data_ptr(), kv_indptr.data_ptr(),
+        kv_indices.data_ptr(), q.data_ptr(), cache.data_ptr(), _dtype_code(cache.dtype), int(page_size),
+        int(bool(write_kv)), cache.shape[0], _stream()), "qkv_prepare")
+    return q
+
+
+def masked_attention(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, ctx, tables, n_heads: int,
+                     n_kv_heads: int, head_dim: int, v_dim: int, scale: float, window: int = 0, chunk: int = 0,
+                     sink: Optional[torch.Tensor] = None) -> None:
+    """Causal attention with optional masks and sink over pages laid out [k | v] with values of size ``v_dim``:
+    ``window`` > 0 keeps the last ``window`` keys, ``chunk`` > 0 the keys of the query's own chunk of positions;
+    ``sink`` (float32 per query head) adds exp(sink) to the softmax denominator.  float32 arithmetic."""
+    _require_cuda(q, out, cache, sink)
+    assert q.stride(1) == 1 and out.is_contiguous() and out.dtype == q.dtype == cache.dtype
+    assert out.shape == (q.shape[0], n_heads * v_dim)
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == n_heads and sink.is_contiguous())
+    _check(load_library().bspec_attention_masked(
+        q.data_ptr(), q.stride(0), out.data_ptr(), cache.data_ptr(), _dtype_code(q.dtype), ctx.qo_indptr.data_ptr(),
+        ctx.positions.data_ptr(), tables.kv_indptr.data_ptr(), tables.kv_indices.data_ptr(), ctx.n_entries,
+        ctx.max_q_len, n_heads, n_kv_heads, head_dim, v_dim, tables.page_size, float(scale), int(window), int(chunk),
+        _ptr(sink), cache.shape[0], _stream()), "attention_masked")
+
+
+# ---------------------------------------------------------------------------- gated delta rule
+
+def delta_prepare(proj: torch.Tensor, b_off: int, a_off: int, conv: torch.Tensor, a_log: torch.Tensor,
+                  dt_bias: torch.Tensor, state: torch.Tensor, tail_off: int, ctx, n_heads: int, n_kv_heads: int,
+                  dim: int, v_dim: int, taps: int, q_scale: float, unit_eps: float):
+    """(mix float32 [n, C], gates float32 [n, 2 H]) from the float32 rows of the fused projection
+    [q | k | v | ... b at b_off | a at a_off]: short causal convolution and silu of the C = 2 G dim + H v_dim
+    channels (inputs before the portion come from ``state[slot, tail_off:]``), unit length of every q and k head
+    (q times ``q_scale``), beta = sigmoid(b) and the decay exp(-exp(A_log) softplus(a + dt_bias))."""
+    _require_cuda(proj, conv, state)
+    n, ld = proj.shape
+    C = 2 * n_kv_heads * dim + n_heads * v_dim
+    assert proj.dtype == torch.float32 and proj.is_contiguous() and state.dtype == torch.float32 and state.is_contiguous()
+    assert conv.shape == (C, taps) and conv.is_contiguous() and conv.dtype == a_log.dtype == dt_bias.dtype
+    assert a_log.numel() == n_heads and dt_bias.numel() == n_heads
+    assert tail_off + (taps - 1) * C <= state.shape[1] and max(b_off, a_off) + n_heads <= ld and C <= ld
+    mix = torch.empty((n, C), dtype=torch.float32, device=proj.device)
+    gates = torch.empty((n, 2 * n_heads), dtype=torch.float32, device=proj.device)
+    _check(load_library().bspec_delta_prepare(
+        proj.data_ptr(), n, ld, int(b_off), int(a_off), conv.data_ptr(), a_log.data_ptr(), dt_bias.data_ptr(),
+        _dtype_code(conv.dtype), state.data_ptr(), state.stride(0), int(tail_off), ctx.qo_indptr.data_ptr(),
+        ctx.tok_entry.data_ptr(), ctx.state_slots.data_ptr(), mix.data_ptr(), gates.data_ptr(), n_heads, n_kv_heads,
+        dim, v_dim, taps, float(q_scale), float(unit_eps), _stream()), "delta_prepare")
+    return mix, gates
+
+
+def delta_recurrence(mix: torch.Tensor, gates: torch.Tensor, proj: torch.Tensor, state: torch.Tensor, tail_off: int,
+                     ctx, n_heads: int, n_kv_heads: int, dim: int, v_dim: int, taps: int) -> torch.Tensor:
+    """The gated delta rule over every entry's portion, per head: S <- g S; u = beta (v - S^T k); S <- S + k u^T;
+    o = S^T q.  ``state[slot, :H * v_dim * dim]`` holds S as [head, value column, key row] and is read and written;
+    ``state[slot, tail_off:]`` receives the portion's last ``taps - 1`` projection rows.  Returns o float32
+    [n, H * v_dim]."""
+    _require_cuda(mix, gates, proj, state)
+    n = mix.shape[0]
+    assert state.stride(0) % 4 == 0 and dim % 4 == 0 and dim <= 256
+    out = torch.empty((n, n_heads * v_dim), dtype=torch.float32, device=mix.device)
+    _check(load_library().bspec_delta_recurrence(
+        mix.data_ptr(), gates.data_ptr(), proj.data_ptr(), proj.shape[1], state.data_ptr(), state.stride(0),
+        int(tail_off), ctx.qo_indptr.data_ptr(), ctx.state_slots.data_ptr(), out.data_ptr(), ctx.n_entries, n_heads,
+        n_kv_heads, dim, v_dim, taps, _stream()), "delta_recurrence")
+    return out
+
+
+def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, n_heads: int, v_dim: int,
+                  out_dtype: torch.dtype) -> torch.Tensor:
+    """o float32 [n, H * V]; gate a float32 view [n, H * V] of rows that may be wider.  Returns
+    o / rms_V(o) * weight * silu(gate) in ``out_dtype``."""
+    _require_cuda(o, gate, weight)
+    n = o.shape[0]
+    assert o.dtype == torch.float32 and o.is_contiguous() and gate.dtype == torch.float32 and gate.stride(1) == 1
+    assert gate.shape == o.shape == (n, n_heads * v_dim) and weight.numel() == v_dim
+    out = torch.empty((n, n_heads * v_dim), dtype=out_dtype, device=o.device)
+    _check(load_library().bspec_gated_rmsnorm(o.data_ptr(), gate.data_ptr(), gate.stride(0), weight.data_ptr(),
+                                              _dtype_code(weight.dtype), out.data_ptr(), _dtype_code(out_dtype), n,
+                                              n_heads, v_dim, float(eps), _stream()), "gated_rmsnorm")
+    return out
+
+
 # ---------------------------------------------------------------------------- matrix products
 
 # Which bfloat16 products run on this package's tcgen05 kernel: "auto" (those with at most TC_GEMM_MAX_M rows),
@@ -580,13 +730,14 @@ def check_status() -> None:
 
 _BOUNDS_REPORTS = ["bspec_bounds_report_elementwise", "bspec_bounds_report_gemm_tcgen05",
                    "bspec_bounds_report_attention_generic", "bspec_bounds_report_attention_bf16",
-                   "bspec_bounds_report_latent", "bspec_bounds_report_latent_mma"]
+                   "bspec_bounds_report_latent", "bspec_bounds_report_latent_mma", "bspec_bounds_report_delta"]
 BOUNDS_CODES = {101: "token id (embedding)", 102: "row (gather)", 103: "block-table slot (rotary + cache append)",
                 104: "page id (rotary + cache append)", 105: "block-table slot (q/k/v product's epilogue)",
                 106: "page id (q/k/v product's epilogue)", 107: "page id (attention over plain loads)",
                 108: "page id (bfloat16 attention over plain loads)", 109: "block-table slot (latent entry append)",
                 110: "page id (latent entry append)", 111: "page id (latent attention over plain loads)",
-                112: "page id (latent attention on the tensor cores)"}
+                112: "page id (latent attention on the tensor cores)", 113: "block-table slot (q/k/v preparation)",
+                114: "page id (q/k/v preparation)"}
 
 
 def bounds_reports() -> list:

@@ -11,6 +11,7 @@ from typing import Callable, Dict
 from ..parts.base import Runtime
 from .decoder import CacheNeed, DecoderModel, LayerCache
 from .llama import build_llama
+from .lupusun import build_lupusun
 from .spec import LayerSpec, ModelSpec, RunEntry, prenorm_layer
 from .vabanex import build_vabanex
 
@@ -30,6 +31,7 @@ def get_model(config, runtime: Runtime) -> DecoderModel:
 
 register_model("LlamaForCausalLM", build_llama)
 register_model("Vabanex", build_vabanex)
+register_model("Lupusun", build_lupusun)
 
 __all__ = ["MODEL_REGISTRY", "register_model", "get_model", "DecoderModel", "LayerCache", "CacheNeed",
-           "ModelSpec", "LayerSpec", "RunEntry", "prenorm_layer", "build_llama", "build_vabanex"]
+           "ModelSpec", "LayerSpec", "RunEntry", "prenorm_layer", "build_llama", "build_lupusun", "build_vabanex"]

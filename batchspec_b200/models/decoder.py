@@ -52,7 +52,7 @@ class DecoderModel:
                 raise ValueError(f"layer {i}: block {layer.block!r} has slots {list(kind.SLOTS)}, "
                                  f"the description gives {list(layer.parts)}")
             self.blocks.append(kind(**{slot: build_part(registry, layer.parts[slot], runtime)
-                                       for slot, registry in kind.SLOTS.items()}))
+                                       for slot, registry in kind.SLOTS.items()}, **layer.block_params))
         self.final_norm = build_part(NORMS, spec.final_norm, runtime)
         self.input_part = build_part(INPUT_PARTS, spec.input_part, runtime) if spec.input_part else None
         self.logits_part = build_part(LOGITS_PARTS, spec.logits_part, runtime) if spec.logits_part else None
@@ -65,6 +65,8 @@ class DecoderModel:
         self.embed: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.caches: List[Optional[LayerCache]] = [None] * len(spec.order)
+        # debugging aid: called as probe(run index, residual after the run, float32 [n, d]) when set
+        self.layer_probe = None
 
     @property
     def graph_safe(self) -> bool:
@@ -131,14 +133,24 @@ class DecoderModel:
             ops.embed(ctx.token_ids, self.embed, resid, s.embed_scale)
         if self.input_part is not None:
             self.input_part.forward(resid, ctx)
-        pending = None
+        first = resid.clone() if any(run.add_input for run in s.order) else None
+        pending, scale = None, 1.0
         for e, run in enumerate(s.order):
-            resid, pending = self.blocks[run.layer].forward(resid, pending, ctx, self.caches[e])
+            if run.add_input:
+                ops.residual_update(resid, pending, scale, first)
+                pending, scale = None, 1.0
+            block = self.blocks[run.layer]
+            resid, pending = block.forward(resid, pending, ctx, self.caches[e], scale)
+            scale = block.residual_mult
+            if self.layer_probe is not None:
+                after = resid.clone()
+                ops.residual_update(after, pending, scale)
+                self.layer_probe(e, after)
         n_out = ctx.n_logit_rows
         if n_out == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=self.runtime.device)
         picked = torch.empty((n_out, s.hidden_size), dtype=torch.float32, device=self.runtime.device)
-        ops.gather_rows_add(resid, pending, ctx.logit_rows, picked)
+        ops.gather_rows_add(resid, pending, ctx.logit_rows, picked, scale)
         z = self.final_norm.forward(picked, None)
         with bucket("lm_head"):
             logits = ops.linear(z, self.head, out_dtype=torch.float32)

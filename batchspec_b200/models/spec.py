@@ -18,6 +18,7 @@ class LayerSpec:
     parts: Dict[str, PartSpec]
     names: Dict[str, str]
     block: str = "prenorm"
+    block_params: Dict[str, object] = field(default_factory=dict)     # constants of the block kind (residual_mult ...)
 
 
 def prenorm_layer(norm1: PartSpec, mixer: PartSpec, norm2: PartSpec, ffn: PartSpec, names: Dict[str, str]) -> LayerSpec:
@@ -30,9 +31,12 @@ class RunEntry:
     """One run of a layer.  ``layer`` indexes ``ModelSpec.layers`` (the same layer
     may be run more than once: shared weights, separate caches).  ``cache_from``
     is None when the run owns a cache of its own, or the index of an EARLIER entry
-    of the order whose cache this run reads without writing."""
+    of the order whose cache this run reads without writing.  ``add_input``: the
+    residual stream as it entered the first run (the embedding after the input part)
+    is added to the stream right before this run."""
     layer: int
     cache_from: Optional[int] = None
+    add_input: bool = False
 
 
 @dataclass

@@ -49,6 +49,9 @@ class CacheSpec:
     policy ``full``: every token's entry is kept while the request lives.
     policy ``window``: only the last ``window`` tokens are ever read; pages that
     lie wholly before the window are given back.
+    policy ``chunk``: a token reads only the tokens of its own chunk of ``window``
+    positions (counted from position 0); pages that lie wholly before the chunk of
+    the next position are given back.
     ``entry_shape`` is the per-token shape of ONE stored tensor, e.g.
     (n_kv_heads, head_dim); ``tensors`` says how many of them a token has: 2 for
     keys and values, 1 for a mixer that stores a single (compressed) entry.
@@ -95,12 +98,12 @@ class Part:
 
 
 class Norm(Part):
-    """``forward(resid, delta, out=None)``: ``resid`` is the float32 residual
-    stream [n, d]; if ``delta`` is given it is first added into ``resid`` in
-    place (the residual sum, in 32-bit); returns the normalised rows in the run
-    dtype."""
+    """``forward(resid, delta, delta_scale=1.0)``: ``resid`` is the float32 residual
+    stream [n, d]; if ``delta`` is given, ``delta_scale * delta`` is first added into
+    ``resid`` in place (the residual sum, in 32-bit); returns the normalised rows in
+    the run dtype."""
 
-    def forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+    def forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor], delta_scale: float = 1.0) -> torch.Tensor:
         raise NotImplementedError
 
 
@@ -178,11 +181,13 @@ class Block:
     arrive as keyword arguments and are kept as attributes of the same names and in
     ``self.parts``.
 
-    ``forward(resid, pending, ctx, cache)`` takes the float32 residual and a
-    not-yet-added branch output (or None) and returns the same pair, so the add
-    can be fused into the next norm."""
+    ``forward(resid, pending, ctx, cache, pending_scale=1.0)`` takes the float32 residual and a
+    not-yet-added branch output (or None) with the factor it is to be added with, and returns the
+    residual and its own last branch output, so the add can be fused into the next norm.  ``residual_mult``
+    is the factor of the branch a block returns."""
     SLOTS: Dict[str, Dict[str, type]] = {}
     MIXER_SLOT = "mixer"
+    residual_mult = 1.0
 
     def __init__(self, **parts):
         missing, extra = set(self.SLOTS) - set(parts), set(parts) - set(self.SLOTS)
@@ -193,7 +198,7 @@ class Block:
         for slot, part in self.parts.items():
             setattr(self, slot, part)
 
-    def forward(self, resid, pending, ctx, cache):
+    def forward(self, resid, pending, ctx, cache, pending_scale: float = 1.0):
         raise NotImplementedError
 
 

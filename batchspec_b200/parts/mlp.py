@@ -15,9 +15,13 @@ from .base import FEED_FORWARDS, FeedForward, ParamSpec, Runtime, register_part
 
 @register_part(FEED_FORWARDS, "swiglu")
 class SwiGLU(FeedForward):
+    """``activation``: what the gate passes through, "silu" (the reference's) or "relu"."""
     graph_safe = True
-    def __init__(self, runtime: Runtime, dim: int, intermediate: int):
+    def __init__(self, runtime: Runtime, dim: int, intermediate: int, activation: str = "silu"):
         self.runtime, self.dim, self.intermediate = runtime, int(dim), int(intermediate)
+        if activation not in ("silu", "relu"):
+            raise ValueError(f"gated feed-forward activation {activation!r} is not known ('silu', 'relu')")
+        self.activation = activation
         self.w13 = self.w2 = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -39,13 +43,13 @@ class SwiGLU(FeedForward):
     def forward(self, x, ctx):
         if self.group:
             with bucket("mlp.gate_up_proj"):
-                m = ops.linear_glu(x, self.w13, self.group)
+                m = ops.linear_glu(x, self.w13, self.group, self.activation)
         else:
             with bucket("mlp.gate_up_proj"):
                 u = ops.linear(x, self.w13)
             m = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
             with bucket("mlp.act"):
-                ops.silu_mul(u, m)
+                (ops.relu_mul if self.activation == "relu" else ops.silu_mul)(u, m)
         with bucket("mlp.down_proj"):
             return ops.linear(m, self.w2)
 

@@ -1,6 +1,7 @@
 """RMSNorm part (batchspec/models/modules/normalization.py:24-39): float32
 x * rsqrt(mean(x^2) + eps), cast to the run dtype, then times the weight.
-Fused with the residual add that precedes it (base_model.py:53,56)."""
+Fused with the residual add that precedes it (base_model.py:53,56).  With ``single_rounding`` the product with the
+weight is taken in float32 too and the result is rounded once."""
 from __future__ import annotations
 
 from typing import Dict, Optional
@@ -9,14 +10,15 @@ import torch
 
 from ..kernels import ops
 from ..profiler import bucket
-from .base import NORMS, Norm, ParamSpec, Runtime, register_part
+from .base import INPUT_PARTS, NORMS, InputPart, Norm, ParamSpec, Runtime, register_part
 
 
 @register_part(NORMS, "rmsnorm")
 class RMSNorm(Norm):
     graph_safe = True
-    def __init__(self, runtime: Runtime, dim: int, eps: float):
+    def __init__(self, runtime: Runtime, dim: int, eps: float, single_rounding: bool = False):
         self.runtime, self.dim, self.eps = runtime, int(dim), float(eps)
+        self.single_rounding = bool(single_rounding)
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -25,10 +27,10 @@ class RMSNorm(Norm):
     def bind(self, params):
         self.weight = params["weight"]
 
-    def forward(self, resid, delta=None):
+    def forward(self, resid, delta=None, delta_scale: float = 1.0):
         out = torch.empty(resid.shape, dtype=self.runtime.dtype, device=resid.device)
         with bucket("norm"):
-            ops.add_rmsnorm(resid, delta, self.weight, self.eps, out)
+            ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, delta_scale, self.single_rounding)
         return out
 
 
@@ -52,8 +54,33 @@ class LayerNorm(Norm):
         if self.bias.dtype != self.weight.dtype:
             self.bias = self.bias.to(self.weight.dtype)
 
-    def forward(self, resid, delta=None):
+    def forward(self, resid, delta=None, delta_scale: float = 1.0):
+        if delta is not None and delta_scale != 1.0:
+            ops.residual_update(resid, delta, delta_scale)
+            delta = None
         out = torch.empty(resid.shape, dtype=self.runtime.dtype, device=resid.device)
         with bucket("norm"):
             ops.add_layernorm(resid, delta, self.weight, self.bias, self.eps, out)
         return out
+
+
+@register_part(INPUT_PARTS, "rmsnorm")
+class InputRMSNorm(InputPart):
+    """RMS norm of the embedding rows, in place on the float32 residual: x / sqrt(mean(x^2) + eps) * w."""
+    graph_safe = True
+
+    def __init__(self, runtime: Runtime, dim: int, eps: float):
+        self.runtime, self.dim, self.eps = runtime, int(dim), float(eps)
+        self.weight: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {"weight": ParamSpec((self.dim,), role="vector", init="ones_normal")}
+
+    def bind(self, params):
+        self.weight = params["weight"]
+
+    def forward(self, resid, ctx) -> None:
+        out = torch.empty_like(resid)
+        with bucket("norm"):
+            ops.add_rmsnorm(resid, None, self.weight, self.eps, out, 1.0, True)
+        resid.copy_(out)

@@ -1,0 +1,94 @@
+"""Grouped-query softmax attention with options that the plain attention part does not have, each a parameter:
+
+* biases on the q, k and v projections (added in float32 to the product's float32 output);
+* values of their own size ``v_dim``;
+* a position encoding over the first numbers of each head, with a magnitude on cosine and sine (YaRN);
+* ``qk_norm_eps``: after the rotation every q and k head is divided by its root mean square (no weight);
+* a mask besides causality: ``chunk`` (a query sees the keys of its own chunk of ``chunk`` positions, counted from
+  position 0 of the request) or ``window`` (the last ``window`` keys);
+* ``sink``: a learned number per query head that enters the softmax denominator as exp(sink), with no key and no
+  value: out_h(i) = sum_j exp(s_ij) v_j / (exp(sink_h) + sum_j exp(s_ij)).
+
+Launch sequence: one product for [Wq; Wk; Wv] with float32 output -> q/k/v preparation (bias, rotation, norms, all
+float32; q in the run dtype, k and v into their cache pages) -> attention over the pages -> output projection.
+A page holds its keys [kv head, row, head_dim] and then its values [kv head, row, v_dim].  With a chunk mask the
+pages that lie wholly before the chunk of the next position are given back."""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..kernels import ops
+from ..profiler import bucket
+from .base import (MIXERS, POSITION_ENCODINGS, CacheSpec, Mixer, ParamSpec, PartSpec, Runtime, build_part,
+                   register_part)
+
+
+@register_part(MIXERS, "sink_attention")
+class SinkAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, runtime: Runtime, dim: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+                 position: PartSpec, v_dim: Optional[int] = None, bias: bool = False,
+                 qk_norm_eps: Optional[float] = None, chunk: Optional[int] = None, window: Optional[int] = None,
+                 sink: bool = False):
+        if n_heads <= 0 or n_kv_heads <= 0 or n_heads % n_kv_heads:
+            raise ValueError(f"n_heads {n_heads} must be a positive multiple of n_kv_heads {n_kv_heads}")
+        self.runtime = runtime
+        self.dim, self.n_heads, self.n_kv_heads, self.head_dim = int(dim), int(n_heads), int(n_kv_heads), int(head_dim)
+        self.v_dim = int(v_dim) if v_dim else self.head_dim
+        if not (0 < self.head_dim <= 256 and 0 < self.v_dim <= 256):
+            raise ValueError(f"attention kernels take head sizes up to 256, got {head_dim} and {self.v_dim}")
+        self.scale, self.bias, self.sink = float(scale), bool(bias), bool(sink)
+        self.qk_norm_eps = float(qk_norm_eps) if qk_norm_eps else 0.0
+        self.chunk, self.window = int(chunk) if chunk else 0, int(window) if window else 0
+        if self.chunk < 0 or self.window < 0 or (self.chunk and self.window):
+            raise ValueError("give a chunk size or a window, both positive, not both")
+        self.position = build_part(POSITION_ENCODINGS, position, runtime)
+        self.wqkv = self.wo = self.b = self.sinks = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        q, k, v = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim, self.n_kv_heads * self.v_dim
+        specs = {"q": ParamSpec((q, self.dim)), "k": ParamSpec((k, self.dim)), "v": ParamSpec((v, self.dim)),
+                 "o": ParamSpec((self.dim, self.n_heads * self.v_dim))}
+        if self.bias:
+            specs.update({"q_bias": ParamSpec((q,), role="vector"), "k_bias": ParamSpec((k,), role="vector"),
+                          "v_bias": ParamSpec((v,), role="vector")})
+        if self.sink:
+            specs["sink"] = ParamSpec((self.n_heads,), role="vector")
+        return specs
+
+    def bind(self, params):
+        self.wqkv = torch.cat([params["q"], params["k"], params["v"]], dim=0).contiguous()
+        self.wo = params["o"].contiguous()
+        if self.bias:
+            self.b = torch.cat([params[n].to(torch.float32) for n in ("q_bias", "k_bias", "v_bias")]).contiguous()
+        if self.sink:
+            self.sinks = params["sink"].to(torch.float32).contiguous()
+
+    def cache_spec(self) -> CacheSpec:
+        policy = "chunk" if self.chunk else ("window" if self.window else "full")
+        span = self.chunk or self.window or None
+        if self.v_dim == self.head_dim:
+            return CacheSpec(policy, (self.n_kv_heads, self.head_dim), span)
+        return CacheSpec(policy, (self.n_kv_heads * (self.head_dim + self.v_dim),), span, tensors=1)
+
+    def forward(self, x, ctx, cache):
+        n = x.shape[0]
+        H, G, hd, vd = self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim
+        tables = ctx.tables[cache.group]
+        pos = self.position
+        with bucket("attn.qkv_proj"):
+            qkv = ops.linear(x, self.wqkv, out_dtype=torch.float32)
+        with bucket("attn.rope"):
+            q = ops.qkv_prepare(qkv, H, G, hd, vd, self.b, getattr(pos, "inv_freq", None),
+                                getattr(pos, "rotary_dim", 0), getattr(pos, "interleaved", False),
+                                getattr(pos, "magnitude", 1.0), self.qk_norm_eps, ctx.positions, ctx.tok_entry,
+                                tables.kv_indptr, tables.kv_indices, cache.kv, tables.page_size, write_kv=cache.owner)
+        out = torch.empty((n, H * vd), dtype=x.dtype, device=x.device)
+        with bucket("attn.compute"):
+            ops.masked_attention(q, out, cache.kv, ctx, tables, H, G, hd, vd, self.scale, self.window, self.chunk,
+                                 self.sinks)
+        with bucket("attn.o_proj"):
+            return ops.linear(out, self.wo)
