@@ -25,7 +25,7 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 30.f ? x : log
 
 // proj [n, ld] float32, columns [q: Gk*dim | k: Gk*dim | v: H*vdim | ... | b: H at b_off | a: H at a_off].
 // conv [C, taps] (C = 2*Gk*dim + H*vdim).  State row of a request: [H*vdim*dim matrix | (taps-1) x C inputs, oldest
-// first].  mix [n, C] and gates [n, 2H] (beta, then g) are float32.
+// first]; a column of the matrix holds dim numbers padded to a multiple of 4.  mix [n, C] and gates [n, 2H] (beta, then g) are float32.
 __global__ void __launch_bounds__(256)
 delta_prepare_kernel(const float* __restrict__ proj, int ld, int b_off, int a_off, const void* __restrict__ conv,
                      const void* __restrict__ a_log, const void* __restrict__ dt_bias, int w_dtype,
@@ -83,6 +83,7 @@ delta_recurrence_kernel(const float* __restrict__ mix, const float* __restrict__
                         const int* __restrict__ qo_indptr, const int* __restrict__ state_slots,
                         float* __restrict__ out, int H, int Gk, int dim, int vdim, int taps) {
   bspec::pdl_prologue(61);
+  const int dimp = (dim + 3) & ~3;                 // a column of S is kept padded to whole float4s; the pad stays 0
   __shared__ __align__(16) float qs[TILE][MAX_DIM];
   __shared__ __align__(16) float ks[TILE][MAX_DIM];
   __shared__ float vs[TILE][COLS];
@@ -107,22 +108,22 @@ delta_recurrence_kernel(const float* __restrict__ mix, const float* __restrict__
   const bool live = j < vdim;
   const int kh = h / (H / Gk);
   float s[R];
-  float* sp = srow + ((size_t)h * vdim + (live ? j : 0)) * dim;
+  float* sp = srow + ((size_t)h * vdim + (live ? j : 0)) * dimp;
 #pragma unroll
   for (int c = 0; c < R / 4; ++c) {
     const int row = 16 * c + 4 * r;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (live && row < dim) v = *reinterpret_cast<const float4*>(sp + row);
+    if (live && row < dimp) v = *reinterpret_cast<const float4*>(sp + row);
     s[4 * c] = v.x; s[4 * c + 1] = v.y; s[4 * c + 2] = v.z; s[4 * c + 3] = v.w;
   }
   for (int t0 = 0; t0 < n; t0 += TILE) {
     const int nt = min(TILE, n - t0);
     __syncthreads();
-    for (int w = threadIdx.x; w < nt * dim; w += blockDim.x) {
-      const int tt = w / dim, d = w - tt * dim;
+    for (int w = threadIdx.x; w < nt * dimp; w += blockDim.x) {
+      const int tt = w / dimp, d = w - tt * dimp;
       const float* row = mix + (size_t)(q_begin + t0 + tt) * C;
-      qs[tt][d] = row[kh * dim + d];
-      ks[tt][d] = row[(Gk + kh) * dim + d];
+      qs[tt][d] = d < dim ? row[kh * dim + d] : 0.f;
+      ks[tt][d] = d < dim ? row[(Gk + kh) * dim + d] : 0.f;
     }
     for (int w = threadIdx.x; w < nt * COLS; w += blockDim.x) {
       const int tt = w / COLS, cc = w - tt * COLS;
@@ -140,7 +141,7 @@ delta_recurrence_kernel(const float* __restrict__ mix, const float* __restrict__
 #pragma unroll
       for (int c = 0; c < R / 4; ++c) {
         const int row = 16 * c + 4 * r;
-        if (row < dim) {
+        if (row < dimp) {
           const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][row]);
           s[4 * c] *= g; s[4 * c + 1] *= g; s[4 * c + 2] *= g; s[4 * c + 3] *= g;
           dk += s[4 * c] * k4.x; dk += s[4 * c + 1] * k4.y; dk += s[4 * c + 2] * k4.z; dk += s[4 * c + 3] * k4.w;
@@ -153,7 +154,7 @@ delta_recurrence_kernel(const float* __restrict__ mix, const float* __restrict__
 #pragma unroll
       for (int c = 0; c < R / 4; ++c) {
         const int row = 16 * c + 4 * r;
-        if (row < dim) {
+        if (row < dimp) {
           const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][row]);
           const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][row]);
           s[4 * c] += k4.x * u; s[4 * c + 1] += k4.y * u; s[4 * c + 2] += k4.z * u; s[4 * c + 3] += k4.w * u;
@@ -169,7 +170,7 @@ delta_recurrence_kernel(const float* __restrict__ mix, const float* __restrict__
 #pragma unroll
     for (int c = 0; c < R / 4; ++c) {
       const int row = 16 * c + 4 * r;
-      if (row < dim) *reinterpret_cast<float4*>(sp + row) = make_float4(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3]);
+      if (row < dimp) *reinterpret_cast<float4*>(sp + row) = make_float4(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3]);
     }
   }
 }
@@ -220,7 +221,7 @@ BSPEC_API int bspec_delta_recurrence(const float* mix, const float* gates, const
                                      const int* state_slots, float* out, int n_entries, int H, int Gk, int dim,
                                      int vdim, int taps, cudaStream_t stream) {
   if (n_entries <= 0) return 0;
-  if (dim <= 0 || dim > MAX_DIM || dim % 4 != 0 || H % Gk != 0 || n_entries > 65535 || H > 65535)
+  if (dim <= 0 || dim > MAX_DIM || H % Gk != 0 || n_entries > 65535 || H > 65535)
     return (int)cudaErrorInvalidValue;
   const dim3 grid((vdim + COLS - 1) / COLS, H, n_entries);
 #define LR(R) BSPEC_LAUNCH((delta_recurrence_kernel<R>), grid, COLS * LANES, 0, stream, mix, gates, proj, ld, state, \

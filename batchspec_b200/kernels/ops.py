@@ -656,12 +656,12 @@ def delta_prepare(proj: torch.Tensor, b_off: int, a_off: int, conv: torch.Tensor
 def delta_recurrence(mix: torch.Tensor, gates: torch.Tensor, proj: torch.Tensor, state: torch.Tensor, tail_off: int,
                      ctx, n_heads: int, n_kv_heads: int, dim: int, v_dim: int, taps: int) -> torch.Tensor:
     """The gated delta rule over every entry's portion, per head: S <- g S; u = beta (v - S^T k); S <- S + k u^T;
-    o = S^T q.  ``state[slot, :H * v_dim * dim]`` holds S as [head, value column, key row] and is read and written;
+    o = S^T q.  ``state[slot, :tail_off]`` holds S as [head, value column, key row padded to a multiple of 4] and is read and written;
     ``state[slot, tail_off:]`` receives the portion's last ``taps - 1`` projection rows.  Returns o float32
     [n, H * v_dim]."""
     _require_cuda(mix, gates, proj, state)
     n = mix.shape[0]
-    assert state.stride(0) % 4 == 0 and dim % 4 == 0 and dim <= 256
+    assert state.stride(0) % 4 == 0 and dim <= 256 and tail_off >= n_heads * v_dim * (-(-dim // 4) * 4)
     out = torch.empty((n, n_heads * v_dim), dtype=torch.float32, device=mix.device)
     _check(load_library().bspec_delta_recurrence(
         mix.data_ptr(), gates.data_ptr(), proj.data_ptr(), proj.shape[1], state.data_ptr(), state.stride(0),

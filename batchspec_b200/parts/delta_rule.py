@@ -31,14 +31,14 @@ class GatedDeltaRule(Mixer):
                  eps: float, unit_eps: float = 1e-6):
         if n_heads <= 0 or n_kv_heads <= 0 or n_heads % n_kv_heads:
             raise ValueError(f"n_heads {n_heads} must be a positive multiple of n_kv_heads {n_kv_heads}")
-        if head_dim % 4 or not 0 < head_dim <= 256 or v_dim <= 0 or taps < 1:
-            raise ValueError(f"the delta rule kernels take key sizes in steps of 4 up to 256, got {head_dim}")
+        if not 0 < head_dim <= 256 or v_dim <= 0 or taps < 1:
+            raise ValueError(f"the delta rule kernels take key sizes up to 256, got {head_dim}")
         self.runtime = runtime
         self.dim, self.n_heads, self.n_kv_heads = int(dim), int(n_heads), int(n_kv_heads)
         self.head_dim, self.v_dim, self.taps = int(head_dim), int(v_dim), int(taps)
         self.eps, self.unit_eps = float(eps), float(unit_eps)
         self.channels = 2 * self.n_kv_heads * self.head_dim + self.n_heads * self.v_dim
-        self.tail_off = self.n_heads * self.v_dim * self.head_dim
+        self.tail_off = self.n_heads * self.v_dim * (-(-self.head_dim // 4) * 4)      # columns padded to float4s
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         qk, v, H = self.n_kv_heads * self.head_dim, self.n_heads * self.v_dim, self.n_heads

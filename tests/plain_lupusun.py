@@ -83,8 +83,11 @@ def attention_mixer(h: torch.Tensor, p: Dict[str, torch.Tensor], m: dict, eps: f
     q = (h @ p["q"].T + p["q.b"]).view(T, H, dim)
     k = (h @ p["k"].T + p["k.b"]).view(T, G, dim)
     v = (h @ p["v"].T + p["v.b"]).view(T, G, vdim)
-    q, k = rms(rotate(q, positions, m["rot"]), eps), rms(rotate(k, positions, m["rot"]), eps)
-    o = chunked_sink_attention(q, k, v, p["sink"], float(m["scale"]), int(m["mask"]["size"]), positions)
+    if m.get("rot") and m["rot"]["dims"]:
+        q, k = rotate(q, positions, m["rot"]), rotate(k, positions, m["rot"])
+    q, k = rms(q, eps), rms(k, eps)
+    size = int(m["mask"]["size"]) if m.get("mask") else 1 << 40              # no mask: one chunk for all positions
+    o = chunked_sink_attention(q, k, v, p["sink"], float(m["scale"]), size, positions)
     return o.reshape(T, H * vdim) @ p["o"].T
 
 
@@ -182,3 +185,31 @@ def forward(config: dict, tensors: Dict[str, torch.Tensor], tokens, dtype=torch.
         if layers_out is not None:
             layers_out.append(x.clone())
     return (rms(x, eps) * W["final.norm"]) @ W["head"].T
+
+
+# ---------------------------------------------------------------------------------------------- a model folder
+def read_tensors(path) -> Dict[str, torch.Tensor]:
+    """A safetensors file: 8-byte little-endian header length, a JSON header, the data."""
+    import json
+    import struct
+    import numpy as np
+    kinds = {"F32": np.float32, "BF16": np.uint16, "I32": np.int32, "F64": np.float64}
+    raw = open(path, "rb").read()
+    (hlen,) = struct.unpack("<Q", raw[:8])
+    out = {}
+    for name, meta in json.loads(raw[8:8 + hlen]).items():
+        if name == "__metadata__":
+            continue
+        b, e = meta["data_offsets"]
+        arr = np.frombuffer(raw[8 + hlen + b:8 + hlen + e], dtype=kinds[meta["dtype"]]).copy()
+        if meta["dtype"] == "BF16":
+            arr = (arr.astype(np.uint32) << 16).view(np.float32)
+        out[name] = torch.from_numpy(arr).reshape(meta["shape"])
+    return out
+
+
+def read_model_folder(folder):
+    import json
+    from pathlib import Path
+    folder = Path(folder)
+    return json.loads((folder / "config.json").read_text()), read_tensors(folder / "model.safetensors")

@@ -1,0 +1,495 @@
+"""The Lupusun design on the GPU against its plain implementation (tests/plain_lupusun.py): every mechanism alone,
+then the engine on whole prompts, decoded tails, portions down to two tokens, mixed batches on a pool so small that
+pages and state slots are used again, chunk edges, and greedy generation through the scheduler.  The configurations
+are made here and differ from each other in every size: heads and groups, key / value / rotated sizes (a key size
+that is no multiple of 4, values wider and narrower than keys), chunk sizes that are no multiples of the page size,
+convolutions of one to four taps, layers with and without a feed-forward, a loop from layer 0, a loop in the middle,
+no loop, branch factors below, at and above 1, and a width that is no multiple of 8."""
+import math
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+import plain_lupusun as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = ["float32", "bfloat16"]
+F64 = torch.float64
+
+
+def _attention(heads, kv_heads, dim, vdim, scale, size, dims, base, scaling=None, ff=None):
+    rot = dict(base=base, dims=dims, **({"scaling": scaling} if scaling else {}))
+    return dict(type="attention", mixer=dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=scale,
+                                             mask=dict(size=size), rot=rot),
+                mlp=dict(kind="dense", ff=ff) if ff else None)
+
+
+def _delta(heads, kv_heads, dim, vdim, conv, ff=None):
+    return dict(type="delta", mixer=dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, conv=conv),
+                mlp=dict(kind="dense", ff=ff) if ff else None)
+
+
+def _config(vocab, width, eps, mult, layers, loop=None):
+    d = dict(architecture="Lupusun", vocab=vocab, width=width, norm=dict(eps=eps), residual_mult=mult, layers=layers)
+    if loop:
+        d["loop"] = dict(zip(("start", "stop", "times"), loop))
+    return d
+
+
+YARN_A = dict(factor=3.0, original=32, fast=8.0, slow=1.0)
+CFG_A = _config(200, 48, 1e-5, 0.5, [_attention(3, 3, 16, 24, 0.3, 10, 8, 5000.0, YARN_A, ff=40),
+                                     _delta(4, 2, 8, 12, 3),
+                                     _attention(4, 1, 12, 12, 0.2, 7, 12, 300.0, None, ff=56)], loop=(0, 2, 3))
+CFG_B = _config(513, 100, 1e-6, 1.0, [_delta(2, 2, 6, 40, 1, ff=36),
+                                      _attention(6, 2, 32, 8, 0.11, 33, 16, 1e6, dict(factor=8.0, original=16, fast=4.0, slow=0.5), ff=52),
+                                      _delta(3, 1, 20, 7, 2)])
+CFG_C = _config(640, 256, 1e-5, 1.3, [_attention(8, 2, 64, 64, 0.1, 128, 64, 100000.0, dict(factor=4.0, original=128, fast=32.0, slow=1.0), ff=192),
+                                      _delta(4, 4, 128, 64, 4, ff=128),
+                                      _attention(2, 2, 128, 128, 0.07, 50, 32, 777.0, None)], loop=(1, 3, 2))
+# attention alone, so that nothing carries a token's content past a chunk's edge
+CFG_EDGE = _config(150, 32, 1e-5, 0.9, [_attention(2, 1, 16, 8, 0.5, 12, 16, 1000.0, None, ff=24),
+                                        _attention(2, 2, 8, 16, 0.4, 12, 4, 50.0, YARN_A)])
+CONFIGS = {"A": (CFG_A, 11, 4), "B": (CFG_B, 12, 8), "C": (CFG_C, 13, 16), "EDGE": (CFG_EDGE, 14, 8)}   # config, seed, page
+LENGTHS = {"A": [1, 6, 23, 70], "B": [2, 9, 41, 130], "C": [3, 64, 150, 333]}
+
+
+def _folder(tmp_path, name, dtype, std=0.08):
+    cfg, seed, _ = CONFIGS[name]
+    stored = torch.float32 if dtype == "float32" else torch.bfloat16
+    return H.make_folder(tmp_path / f"l{name}_{dtype}", cfg, seed, dtype=stored, std=std)
+
+
+def _engine(folder, dtype, page_size, num_pages, max_requests=8):
+    from batchspec_b200.engine import Engine
+    eng = Engine(dtype=dtype, device=DEV)
+    eng.load_model(model_dir=folder)
+    eng.setup_caches(max_batch_size=max_requests, page_size=page_size, num_pages=num_pages)
+    return eng
+
+
+def _oracle(folder, tokens):
+    cfg, w = P.read_model_folder(folder)
+    return P.forward(cfg, w, tokens, dtype=F64).numpy()
+
+
+def _requests(name):
+    cfg, seed, _ = CONFIGS[name]
+    return {f"r{i}": H.random_tokens(n, cfg["vocab"], 100 * seed + i) for i, n in enumerate(LENGTHS[name])}
+
+
+def _rows_agree(a, b, dtype):
+    for k in a:
+        assert np.abs(a[k] - b[k]).max() <= H.TOL[dtype] * np.abs(a[k]).max(), k
+
+
+def _tol(dtype):
+    return 2e-5 if dtype == torch.float32 else 2e-2
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from batchspec_b200.kernels import ops as o
+    o.load_library()
+    return o
+
+
+def _i32(x):
+    return torch.tensor(list(x), dtype=torch.int32, device=DEV)
+
+
+# ------------------------------------------------------------------------------------------- mechanisms alone
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,d", [(3, 96), (5, 50), (2, 4096), (1, 18000)])
+def test_norm_with_one_rounding_and_scaled_branches(ops, dtype, n, d):
+    g = torch.Generator(device=DEV).manual_seed(d)
+    resid = torch.randn(n, d, device=DEV, generator=g) * 3
+    delta = torch.randn(n, d, device=DEV, generator=g).to(dtype)
+    extra = torch.randn(n, d, device=DEV, generator=g)
+    w = (1 + 0.3 * torch.randn(d, device=DEV, generator=g)).to(dtype)
+    r = resid.clone()
+    out = torch.full((n, d), float("nan"), device=DEV, dtype=dtype)
+    ops.add_rmsnorm(r, delta, w, 1e-3, out, 0.7, True)
+    x = resid.double() + 0.7 * delta.double()
+    want = P.rms(x, 1e-3) * w.double()
+    assert torch.allclose(r.double(), x, atol=1e-6)
+    assert (out.double() - want).abs().max() <= (1e-5 if dtype == torch.float32 else 2 ** -8) * want.abs().max()
+    if dtype == torch.bfloat16:                    # one rounding: the nearest bfloat16 of the float32 result
+        assert (out == (P.rms(r, 1e-3) * w.float()).to(dtype)).float().mean() > 0.99
+    r2 = resid.clone()
+    ops.residual_update(r2, delta, -1.5, extra)
+    assert torch.allclose(r2.double(), resid.double() - 1.5 * delta.double() + extra.double(), atol=1e-5)
+    rows = _i32([n - 1, 0])
+    picked = torch.empty(2, d, device=DEV)
+    ops.gather_rows_add(resid, delta, rows, picked, 0.25)
+    assert torch.allclose(picked.double(), (resid.double() + 0.25 * delta.double())[[n - 1, 0]], atol=1e-5)
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 80, 64), (8, 448, 256), (5, 176, 72), (40, 256, 96), (3, 52, 64)])
+def test_relu_gate_in_the_product_and_alone(ops, M, I, K):
+    g = torch.Generator(device=DEV).manual_seed(M + I)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    wg = (2.0 * torch.randn(I, K, device=DEV, generator=g) / K ** 0.5).bfloat16()
+    wu = (2.0 * torch.randn(I, K, device=DEV, generator=g) / K ** 0.5).bfloat16()
+    want = torch.relu(x.double() @ wg.double().T) * (x.double() @ wu.double().T)
+    if I % ops.GLU_GROUP == 0:
+        got = ops.linear_glu(x, ops.interleave_gate_up(wg, wu), activation="relu")
+    else:
+        got = torch.empty(M, I, device=DEV, dtype=torch.bfloat16)
+        ops.relu_mul(ops.linear(x, torch.cat([wg, wu])), got)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert (want == 0).any() and (got.double() - want).abs().max() <= 3e-2 * max(1.0, want.abs().max().item())
+    u = torch.randn(M, 2 * I, device=DEV, generator=g)
+    m = torch.empty(M, I, device=DEV)
+    ops.relu_mul(u, m)
+    assert torch.equal(m, torch.relu(u[:, :I]) * u[:, I:])
+
+
+def _paged(ops, dtype, Hq, G, hd, vd, ps, q_lens, kv_lens, seed):
+    """Random k and v of every request in pages handed out in scrambled order."""
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    ks = [torch.randn(L, G, hd, device=DEV, generator=g).to(dtype) for L in kv_lens]
+    vs = [torch.randn(L, G, vd, device=DEV, generator=g).to(dtype) for L in kv_lens]
+    pages_per = [-(-L // ps) for L in kv_lens]
+    n_pages = sum(pages_per) + 3
+    perm = torch.randperm(n_pages - 1, generator=torch.Generator().manual_seed(seed + 1))[:sum(pages_per)]
+    cache = torch.randn(n_pages, ps * G * (hd + vd), device=DEV, generator=g).to(dtype)
+    indptr = [0] + list(np.cumsum(pages_per))
+    qo = [0] + list(np.cumsum(q_lens))
+    pos = torch.cat([torch.arange(L - q, L) for q, L in zip(q_lens, kv_lens)]).to(DEV, torch.int32)
+    ent = torch.cat([torch.full((q,), i) for i, q in enumerate(q_lens)]).to(DEV, torch.int32)
+    ctx = SimpleNamespace(qo_indptr=_i32(qo), positions=pos, tok_entry=ent, n_entries=len(q_lens), n_tokens=sum(q_lens),
+                          max_q_len=max(q_lens), max_kv_len=max(kv_lens), extras={"min_q_len": min(q_lens)})
+    tables = SimpleNamespace(kv_indptr=_i32(indptr), kv_indices=perm.to(DEV, torch.int32), page_size=ps)
+
+    def fill():
+        for e, L in enumerate(kv_lens):
+            for p in range(L):
+                page = cache[int(perm[indptr[e] + p // ps])]
+                page[:G * ps * hd].view(G, ps, hd)[:, p % ps] = ks[e][p]
+                page[G * ps * hd:].view(G, ps, vd)[:, p % ps] = vs[e][p]
+    return ks, vs, cache, ctx, tables, fill, qo
+
+
+def _attention_case(ops, dtype, Hq, G, hd, vd, ps, chunk, q_lens, kv_lens, sink, spike=None, seed=0):
+    ks, vs, cache, ctx, tables, fill, qo = _paged(ops, dtype, Hq, G, hd, vd, ps, q_lens, kv_lens, seed)
+    g = torch.Generator(device=DEV).manual_seed(seed + 5)
+    n = sum(q_lens)
+    q = torch.randn(n, Hq, hd, device=DEV, generator=g)
+    if spike is not None:                          # one key whose score with the last query of a request stands out
+        e, key, head = spike
+        t = qo[e] + q_lens[e] - 1
+        q[t, head] = 0
+        q[t, head, hd - 1] = 40.0
+        ks[e][:, :, hd - 1] = ks[e][:, :, hd - 1].clamp(-1, 1)
+        ks[e][key, head // (Hq // G), hd - 1] = 30.0
+    q = q.to(dtype)
+    fill()
+    out = torch.full((n, Hq * vd), float("nan"), device=DEV, dtype=dtype)
+    ops.masked_attention(q.view(n, Hq * hd), out, cache, ctx, tables, Hq, G, hd, vd, 0.25, 0, chunk, sink)
+    torch.cuda.synchronize()
+    want = torch.empty(n, Hq, vd, dtype=F64)
+    for e, (ql, L) in enumerate(zip(q_lens, kv_lens)):
+        pos = torch.arange(L)
+        full = P.chunked_sink_attention(
+            torch.cat([torch.zeros(L - ql, Hq, hd, dtype=F64), q[qo[e]:qo[e + 1]].double().cpu()]), ks[e].double().cpu(),
+            vs[e].double().cpu(), (sink.double().cpu() if sink is not None else torch.full((Hq,), -1e30, dtype=F64)),
+            0.25, chunk or (1 << 40), pos)
+        want[qo[e]:qo[e + 1]] = full[L - ql:]
+    return out.double().cpu().view(n, Hq, vd), want, vs
+
+
+ATTENTION_SHAPES = [
+    # query heads, kv heads, key size, value size, page, chunk, q_lens, kv_lens
+    (3, 3, 16, 24, 4, 10, [5, 1, 2], [5, 9, 30]),
+    (4, 1, 12, 12, 1, 7, [1, 1, 7], [40, 1, 7]),
+    (6, 2, 32, 8, 8, 33, [3, 34], [70, 67]),
+    (8, 2, 64, 64, 16, 128, [1, 1, 1, 1], [300, 17, 128, 129]),
+    (2, 2, 128, 40, 16, 50, [70, 2, 1], [200, 5, 333]),
+    (5, 5, 20, 256, 8, 0, [9, 1], [40, 200]),                      # no chunk mask
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("with_sink", [True, False])
+@pytest.mark.parametrize("shape", ATTENTION_SHAPES, ids=lambda s: f"H{s[0]}G{s[1]}d{s[2]}v{s[3]}ps{s[4]}c{s[5]}")
+def test_chunk_masked_attention_with_a_sink(ops, dtype, shape, with_sink):
+    Hq = shape[0]
+    sink = torch.linspace(-2.0, 3.0, Hq, device=DEV) if with_sink else None
+    got, want, _ = _attention_case(ops, dtype, *shape, sink=sink, seed=shape[2])
+    assert not torch.isnan(got).any()
+    assert (got - want).abs().max() <= (2e-5 if dtype == torch.float32 else 2.5e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("key", [0, 511, 512, 513, 527, 528, 1023, 1024, 1025, 1100, 1299])
+def test_one_key_decides_inside_its_chunk_and_is_unseen_outside(ops, dtype, key):
+    """The last query of a request of 1300 tokens (chunks of 512: it sees keys 1024 .. 1299) scores one key far above
+    all others.  Inside the chunk (its first key, page borders, deep inside, the query's own) that key's value comes
+    back; outside (the key just before the chunk, far back, the first of the request) nothing changes.  Decoded
+    alone and as the end of a portion that crosses the chunk's edge."""
+    for q_lens in ([1, 1], [3, 300]):
+        sink = torch.tensor([0.5, -0.5, 0.0, 1.0], device=DEV)
+        got, want, vs = _attention_case(ops, dtype, 4, 2, 32, 48, 16, 512, q_lens, [90, 1300], sink, spike=(1, key, 3),
+                                        seed=key)
+        t = sum(q_lens) - 1
+        assert (got - want).abs().max() <= (1e-4 if dtype == torch.float32 else 2.5e-2)
+        hit = (got[t, 3] - vs[1][key, 1].double().cpu()).abs().max() < 0.05
+        assert hit == (key >= 1024), key
+
+
+def test_a_huge_sink_takes_all_the_weight(ops):
+    sink = torch.tensor([60.0, -60.0], device=DEV)
+    got, want, _ = _attention_case(ops, torch.float32, 2, 2, 16, 16, 4, 6, [4, 1], [4, 11], sink, seed=3)
+    assert got[:, 0].abs().max() < 1e-12 and got[:, 1].abs().max() > 1e-2 and (got - want).abs().max() < 2e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hq,G,hd,vd,rot,ps", [(3, 3, 16, 24, 8, 4), (4, 1, 12, 12, 12, 8), (8, 2, 64, 64, 32, 16),
+                                               (2, 2, 128, 40, 0, 16), (5, 5, 20, 256, 4, 1)])
+def test_bias_rotation_norm_and_append(ops, dtype, Hq, G, hd, vd, rot, ps):
+    eps = 1e-3
+    rotd = dict(base=300.0, dims=rot, scaling=dict(factor=5.0, original=32, fast=6.0, slow=1.0))
+    lens, starts = [3, 1, 9], [0, 70001, 2]                      # positions the portions begin at
+    n = sum(lens)
+    g = torch.Generator(device=DEV).manual_seed(hd)
+    width = (Hq + G) * hd + G * vd
+    qkv = torch.randn(n, width, device=DEV, generator=g) * 2
+    bias = torch.randn(width, device=DEV, generator=g).to(dtype)
+    table, mag = None, 1.0
+    if rot:
+        f, mag = P.yarn_frequencies(rotd)
+        table = ops.rope_frequency_table(f, DEV)
+    pos = torch.cat([torch.arange(s, s + L) for s, L in zip(starts, lens)])
+    ent = torch.cat([torch.full((L,), i) for i, L in enumerate(lens)]).to(DEV, torch.int32)
+    pages_per = [-(-(s + L) // ps) for s, L in zip(starts, lens)]
+    indptr = [0] + list(np.cumsum(pages_per))
+    indices = torch.randperm(sum(pages_per), generator=torch.Generator().manual_seed(1)).to(DEV, torch.int32)
+    cache = torch.zeros(sum(pages_per), ps * G * (hd + vd), device=DEV, dtype=dtype)
+    q = ops.qkv_prepare(qkv, Hq, G, hd, vd, bias, table, rot, False, mag, eps, pos.to(DEV, torch.int32), ent,
+                        _i32(indptr), indices, cache, ps)
+    x = qkv.double().cpu() + bias.double().cpu()
+    qw = x[:, :Hq * hd].view(n, Hq, hd)
+    kw = x[:, Hq * hd:(Hq + G) * hd].view(n, G, hd)
+    vw = x[:, (Hq + G) * hd:].view(n, G, vd)
+    if rot:
+        qw, kw = P.rotate(qw, pos, rotd), P.rotate(kw, pos, rotd)
+    qw, kw = P.rms(qw, eps), P.rms(kw, eps)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert (q.double().cpu().view(n, Hq, hd) - qw).abs().max() <= tol * qw.abs().max()
+    for t in range(n):
+        e, p = int(ent[t]), int(pos[t])
+        page = cache[int(indices[indptr[e] + p // ps])].double().cpu()
+        assert (page[:G * ps * hd].view(G, ps, hd)[:, p % ps] - kw[t]).abs().max() <= tol * kw.abs().max()
+        assert (page[G * ps * hd:].view(G, ps, vd)[:, p % ps] - vw[t]).abs().max() <= tol * vw.abs().max()
+    assert int((cache != 0).sum()) <= n * G * (hd + vd)          # nothing else was written
+
+
+@pytest.mark.parametrize("Hh,G,dk,dv,taps", [(4, 2, 8, 12, 3), (2, 2, 6, 40, 1), (3, 1, 20, 7, 2), (4, 4, 128, 64, 4),
+                                             (2, 1, 256, 33, 4), (8, 8, 64, 128, 2)])
+def test_delta_rule_kernels_over_portions_and_reused_slots(ops, Hh, G, dk, dv, taps):
+    """Three requests fed in portions of unequal sizes through the three kernels, against the plain convolution,
+    unit lengths, gates, recurrence and gated norm over each whole sequence; then a slot is cleared and used by a
+    new request, which must not see what the old one left."""
+    C = 2 * G * dk + Hh * dv
+    ld = C + Hh * dv + 2 * Hh + 3
+    b_off, a_off, g_off = ld - 2 * Hh - 1, ld - Hh - 1, C
+    tail_off = Hh * dv * (-(-dk // 4) * 4)
+    size = -(-(tail_off + (taps - 1) * C) // 4) * 4
+    gen = torch.Generator(device=DEV).manual_seed(dk + dv)
+    conv = torch.randn(C, taps, device=DEV, generator=gen) * 0.7
+    a_log, dt_bias = torch.randn(Hh, device=DEV, generator=gen), torch.randn(Hh, device=DEV, generator=gen)
+    norm_w = 1 + 0.3 * torch.randn(dv, device=DEV, generator=gen)
+    state = torch.zeros(5, size, device=DEV)
+    slots = {"a": 2, "b": 0, "c": 4}
+    steps = [dict(a=5, b=1, c=2), dict(a=1, c=1), dict(b=11, a=2, c=1), dict(c=1), dict(c=9, a=1)]
+    total = {r: sum(s.get(r, 0) for s in steps) for r in slots}
+    proj = {r: torch.randn(total[r], ld, device=DEV, generator=gen) for r in slots}
+    got = {r: [] for r in slots}
+    at = {r: 0 for r in slots}
+
+    def run(step, proj, at):
+        rows = torch.cat([proj[r][at[r]:at[r] + k] for r, k in step.items()]).contiguous()
+        lens = list(step.values())
+        ctx = SimpleNamespace(qo_indptr=_i32([0] + list(np.cumsum(lens))), n_entries=len(lens),
+                              tok_entry=torch.cat([torch.full((k,), i) for i, k in enumerate(lens)]).to(DEV, torch.int32),
+                              state_slots=_i32([slots[r] for r in step]))
+        mix, gates = ops.delta_prepare(rows, b_off, a_off, conv, a_log, dt_bias, state, tail_off, ctx, Hh, G, dk, dv,
+                                       taps, dk ** -0.5, 1e-6)
+        o = ops.delta_recurrence(mix, gates, rows, state, tail_off, ctx, Hh, G, dk, dv, taps)
+        y = ops.gated_rmsnorm(o, rows[:, g_off:g_off + Hh * dv], norm_w, 1e-4, Hh, dv, torch.float32)
+        return y, lens
+
+    def plain(x):
+        x = x.double().cpu()
+        T = x.shape[0]
+        y = P.silu(P.short_conv(x[:, :C], conv.double().cpu()))
+        q = (P.unit(y[:, :G * dk].view(T, G, dk)) * dk ** -0.5).repeat_interleave(Hh // G, dim=1)
+        k = P.unit(y[:, G * dk:2 * G * dk].view(T, G, dk)).repeat_interleave(Hh // G, dim=1)
+        v = y[:, 2 * G * dk:].view(T, Hh, dv)
+        beta = torch.sigmoid(x[:, b_off:b_off + Hh])
+        g = torch.exp(-torch.exp(a_log.double().cpu()) * P.softplus(x[:, a_off:a_off + Hh] + dt_bias.double().cpu()))
+        o = P.gated_delta_rule(q, k, v, beta, g)
+        return (P.rms(o, 1e-4) * norm_w.double().cpu() * P.silu(x[:, g_off:g_off + Hh * dv]).view(T, Hh, dv)).reshape(T, -1)
+
+    for step in steps:
+        y, lens = run(step, proj, at)
+        o = 0
+        for r, k in step.items():
+            got[r].append(y[o:o + k])
+            at[r] += k
+            o += k
+    for r in slots:
+        want = plain(proj[r])
+        assert (torch.cat(got[r]).double().cpu() - want).abs().max() <= 2e-4 * max(1.0, want.abs().max().item()), r
+    assert not state[1].any() and not state[3].any()             # the slots of no request were never written
+    # a new request in a's slot, cleared as the cache manager clears it at admission
+    state[slots["a"]].zero_()
+    fresh = {"a": torch.randn(7, ld, device=DEV, generator=gen)}
+    y1, _ = run(dict(a=3), fresh, dict(a=0))
+    y2, _ = run(dict(a=4), fresh, dict(a=3))
+    want = plain(fresh["a"])
+    assert (torch.cat([y1, y2]).double().cpu() - want).abs().max() <= 2e-4 * max(1.0, want.abs().max().item())
+
+
+# ------------------------------------------------------------------------------------------- the engine
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_whole_tail_portions(tmp_path, name, dtype):
+    cfg, seed, page = CONFIGS[name]
+    folder = _folder(tmp_path, name, dtype)
+    reqs = _requests(name)
+    longest = max(len(t) for t in reqs.values())
+    eng = _engine(folder, dtype, page, -(-longest // page) + 1)
+    for rid, toks in reqs.items():
+        one = {rid: toks}
+        got = H.run_steps_in_process(eng, H.whole(rid, toks))
+        H.compare_with_oracle(got, folder, one, dtype, oracle=_oracle)
+        got_tail = H.run_steps_in_process(eng, H.tail_decoded(rid, toks, tail=40))
+        H.compare_with_oracle(got_tail, folder, one, dtype, oracle=_oracle)
+        got_port = H.run_steps_in_process(eng, H.portions(rid, toks, [7, 2, 16, 3, 2, 5, 2, 31]))
+        H.compare_with_oracle(got_port, folder, one, dtype, oracle=_oracle)
+        _rows_agree(got, got_tail, dtype)
+        _rows_agree(got, got_port, dtype)
+    assert all(g.pool.num_held == 0 for g in eng.cache.groups)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_token_by_token_from_the_first_token(tmp_path, name, dtype):
+    """A whole request decoded one token at a time (the first tokens of a sequence, every page border and chunk
+    edge, the convolutions' first inputs, long decoding) against the whole prompt in one step."""
+    cfg, seed, page = CONFIGS[name]
+    folder = _folder(tmp_path, name, dtype)
+    toks = H.random_tokens(150, cfg["vocab"], 4)
+    eng = _engine(folder, dtype, page, 40)
+    got = H.run_steps_in_process(eng, H.portions("t", toks, [1]))
+    H.compare_with_oracle(got, folder, {"t": toks}, dtype, oracle=_oracle)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_mixed_requests_reuse_pages_and_slots(tmp_path, name, dtype):
+    cfg, seed, page = CONFIGS[name]
+    folder = _folder(tmp_path, name, dtype)
+    base = _requests(name)
+    reqs = dict(base)
+    for i, (rid, toks) in enumerate(base.items()):          # twice as many requests as there are slots
+        reqs[f"s{i}"] = H.random_tokens(max(2, len(toks) // 2 + 3), cfg["vocab"], 999 + i)
+    steps = H.mixed(reqs, seed=seed + 7, max_live=4)
+    max_tokens = H.max_live_tokens(steps, round_to=page)
+    eng = _engine(folder, dtype, page, max_tokens // page, max_requests=4)
+    got = H.run_steps_in_process(eng, steps)
+    assert sum(-(-len(t) // page) for t in reqs.values()) > eng.cache.groups[0].pool.num_pages
+    H.compare_with_oracle(got, folder, reqs, dtype, oracle=_oracle)
+    alone = _engine(folder, dtype, page, -(-max(len(t) for t in reqs.values()) // page) + 1)
+    for rid in ("r2", "r3"):                                # every request alone gives the same rows as in the batch
+        one = H.run_steps_in_process(alone, H.whole(rid, reqs[rid]))
+        _rows_agree(one, {k: got[k] for k in one}, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_run_program(tmp_path, dtype):
+    cfg, seed, page = CONFIGS["B"]
+    folder = _folder(tmp_path, "B", dtype)
+    reqs = _requests("B")
+    steps = H.mixed(reqs, seed=3, max_live=4)
+    got = H.run_trace_subprocess(folder, dtype, steps, tmp_path / "out", H.max_live_tokens(steps, round_to=64))
+    H.compare_with_oracle(got, folder, reqs, dtype, oracle=_oracle)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_token_before_the_chunk_is_unseen_and_the_chunks_first_is_seen(tmp_path, dtype):
+    """A model of attention layers alone (chunks of 12 positions): changing the token just before a chunk changes no
+    logits inside the chunk, bit for bit; changing the chunk's first token changes its last position's.  As one
+    prompt, decoded token by token, and in portions that cross the edge in the middle of a page."""
+    cfg, seed, page = CONFIGS["EDGE"]
+    folder = _folder(tmp_path, "EDGE", dtype, std=0.3)
+    base = H.random_tokens(48, cfg["vocab"], 2)
+    eng = _engine(folder, dtype, page, 12)
+    for make in (lambda t: H.whole("e", t), lambda t: H.portions("e", t, [1]), lambda t: H.portions("e", t, [10, 3, 2, 9])):
+        ref = H.run_steps_in_process(eng, make(base))
+        H.compare_with_oracle(ref, folder, {"e": base}, dtype, oracle=_oracle)
+        for where, seen in ((35, False), (36, True), (23, False), (0, False)):
+            toks = list(base)
+            toks[where] = (toks[where] + 1) % cfg["vocab"]
+            got = H.run_steps_in_process(eng, make(toks))
+            same = all(np.array_equal(got[("e", p)], ref[("e", p)]) for p in range(36, 48))
+            assert same == (not seen), (where, seen)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_far_token_decides_the_logits_through_the_state(tmp_path, dtype):
+    """With weights that make the mixers matter, changing ONE token far back (the first, one at a page border, one
+    deep inside) changes the last position's logits in the oracle: only the recurrent state carries it across the
+    chunks.  The engine follows, decoded alone and as the end of a portion."""
+    cfg, seed, page = CONFIGS["A"]
+    stored = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = H.make_folder(tmp_path / "far", cfg, 21, dtype=stored, std=0.15)
+    base = H.random_tokens(260, cfg["vocab"], 8)
+    eng = _engine(folder, dtype, page, 70)
+    ref0 = _oracle(folder, base)[-1]
+    moved = []
+    for where in (0, 3, 4, 127, 128, 200):
+        toks = list(base)
+        toks[where] = (toks[where] + 17) % cfg["vocab"]
+        ref = _oracle(folder, toks)
+        moved.append(np.abs(ref[-1] - ref0).max() / np.abs(ref0).max())
+        for steps in (H.tail_decoded("f", toks, tail=3), H.portions("f", toks, [250, 10])):
+            got = H.run_steps_in_process(eng, steps)
+            err = np.abs(got[("f", len(toks) - 1)] - ref[-1]).max() / np.abs(ref).max()
+            assert err <= H.TOL[dtype], (where, err)
+    assert max(moved) > 1e-3, "no far token moved the last logits: the weights hide what this test is for"
+
+
+def test_generation_through_the_scheduler(tmp_path):
+    """Greedy generation through Engine.generate (scheduler, portions, captured decode steps) gives the tokens that
+    the oracle's argmax gives, token by token, for requests of unequal length under page pressure."""
+    from batchspec_b200.engine import Engine
+    from batchspec_b200.engine.sequence import Sequence
+    cfg, seed, page = CONFIGS["A"]
+    folder = H.make_folder(tmp_path / "gen", cfg, 31, dtype=torch.float32, std=0.2)
+    prompts = [H.random_tokens(n, cfg["vocab"], 50 + n) for n in (3, 19, 42, 7, 64)]
+    for graphs in (True, False):
+        eng = Engine(dtype="float32", device=DEV)
+        eng.load_model(model_dir=folder)
+        eng.use_cuda_graphs = graphs
+        eng.setup_caches(max_batch_size=3, max_seq_length=96, page_size=page, prefill_chunk_size=16, num_pages=50)
+        eng.setup_sampling_params(temperature=0.0)
+        seqs = [Sequence(i, list(p), max_new_tokens=12) for i, p in enumerate(prompts)]
+        done = {s.seq_id: s for s in eng.generate(seqs)}
+        for i, p in enumerate(prompts):
+            toks = list(p)
+            for k in range(12):
+                ref = _oracle(folder, toks)[-1]
+                top2 = np.sort(ref)[-2:]
+                nxt = done[i].output_ids[k]
+                if top2[1] - top2[0] > 1e-3 * np.abs(ref).max():
+                    assert nxt == int(ref.argmax()), (graphs, i, k)
+                toks.append(nxt)
