@@ -212,7 +212,8 @@ __device__ __forceinline__ void decode_finish(float* scratch_smem, int* s_last, 
                                               float (&o)[HD / 8][4], const TileGeom& t, int row0, int g, int e, int rt,
                                               int split, int n_splits, int row_tiles, int Hq, int Hkv,
                                               __nv_bfloat16* __restrict__ out, float* __restrict__ o_part,
-                                              float* __restrict__ ml_part, int* __restrict__ tile_counters) {
+                                              float* __restrict__ ml_part, int* __restrict__ tile_counters,
+                                              const float* __restrict__ sink_l2) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -256,6 +257,7 @@ __device__ __forceinline__ void decode_finish(float* scratch_smem, int* s_last, 
     const int r = row0 + row, qi = r / t.G, h = g * t.G + (r - qi * t.G);
     const size_t th = (size_t)(t.q_begin + qi) * Hq + h;
     if (n_splits == 1) {
+      lt = bspec::with_sink(lt, mt, sink_l2, h);
       out[th * HD + col] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
     } else {
       o_part[(th * n_splits + split) * HD + col] = acc;
@@ -289,6 +291,7 @@ __device__ __forceinline__ void decode_finish(float* scratch_smem, int* s_last, 
       Wt[sp * 16 + row] = f;
       lt += __ldcg(ml_part + (th * n_splits + sp) * 2 + 1) * f;
     }
+    lt = bspec::with_sink(lt, mt, sink_l2, h);
     Inv[row] = lt > 0.f ? 1.f / lt : 0.f;
   }
   bar_consumers();
@@ -316,7 +319,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, 
                    const __nv_bfloat16* __restrict__ cache, const int* __restrict__ qo_indptr,
                    const int* __restrict__ positions, const int* __restrict__ kv_indptr,
                    const int* __restrict__ kv_indices, int Hq, int Hkv, int page_size, float scale_log2, int window,
-                   int n_splits, int row_tiles, int max_q_short, long long n_pages) {
+                   int n_splits, int row_tiles, int max_q_short, long long n_pages,
+                    const float* __restrict__ sink_l2) {
   bspec::pdl_prologue(8);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [16][HD]
@@ -333,7 +337,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qi_lo = row0 / t.G, qi_hi = min(t.q_len - 1, (row0 + 15) / t.G);
   const int hi_key = t.pos0 + qi_hi;
-  const int lo_key = window > 0 ? max(0, t.pos0 + qi_lo - window + 1) : 0;
+  const int lo_key = bspec::mask_lo(t.pos0 + qi_lo, window);
   const int lo_al = (lo_key / KT) * KT;
   const int n_keys = hi_key + 1 - lo_al;
   const int chunk = ((((n_keys + n_splits - 1) / n_splits) + KT - 1) / KT) * KT;
@@ -349,7 +353,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, 
     const int row = row0 + (lane >> 2) + 8 * r;
     const int qi = row / t.G;
     lim[r] = row < t.rows_total ? t.pos0 + qi : -1;
-    lo[r] = window > 0 ? max(0, t.pos0 + qi - window + 1) : 0;
+    lo[r] = bspec::mask_lo(t.pos0 + qi, window);
   }
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   float o[HD / 8][4];
@@ -399,7 +403,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, 
     }
   }
   decode_finish<HD>(reinterpret_cast<float*>(KV), &s_last, m, l, o, t, row0, g, e, rt, split, n_splits, row_tiles, Hq,
-                    Hkv, out, o_part, ml_part, tile_counters);
+                    Hkv, out, o_part, ml_part, tile_counters, sink_l2);
 }
 
 // ------------------------------------------------------------------------------------ decode, K/V through TMA
@@ -419,7 +423,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
                        float* __restrict__ ml_part, int* __restrict__ tile_counters, int* __restrict__ status,
                        const int* __restrict__ qo_indptr, const int* __restrict__ positions,
                        const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, int Hq, int Hkv,
-                       int page_size, float scale_log2, int window, int n_splits, int row_tiles, int max_q_short) {
+                       int page_size, float scale_log2, int window, int n_splits, int row_tiles, int max_q_short,
+                    const float* __restrict__ sink_l2) {
   // The step's metadata (lengths, positions, block tables) was uploaded before the step's first kernel, and every
   // cached key below the first new token was written by earlier steps: the producer may fetch those tiles while
   // the kernel before this one (which writes q and the new tokens' keys and values) is still running.
@@ -446,7 +451,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qi_lo = row0 / t.G, qi_hi = min(t.q_len - 1, (row0 + 15) / t.G);
   const int hi_key = t.pos0 + qi_hi;
-  const int lo_key = window > 0 ? max(0, t.pos0 + qi_lo - window + 1) : 0;
+  const int lo_key = bspec::mask_lo(t.pos0 + qi_lo, window);
   const int lo_al = (lo_key / KT) * KT;
   const int n_keys = hi_key + 1 - lo_al;
   const int chunk = ((((n_keys + n_splits - 1) / n_splits) + KT - 1) / KT) * KT;
@@ -524,7 +529,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
     const int row = row0 + (lane >> 2) + 8 * r;
     const int qi = row / t.G;
     lim[r] = row < t.rows_total ? t.pos0 + qi : -1;
-    lo[r] = window > 0 ? max(0, t.pos0 + qi - window + 1) : 0;
+    lo[r] = bspec::mask_lo(t.pos0 + qi, window);
   }
   if (n_tiles > 0) {
     load_q_tile<HD>(Qs, q, q_row_stride, t, row0, 16);
@@ -552,7 +557,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
   bar_consumers();                        // every warp is done with the stages (or gave up)
   if (*abort_flag) return;
   decode_finish<HD>(reinterpret_cast<float*>(KV), s_last, m, l, o, t, row0, g, e, rt, split, n_splits, row_tiles, Hq,
-                    Hkv, out, o_part, ml_part, tile_counters);
+                    Hkv, out, o_part, ml_part, tile_counters, sink_l2);
 }
 
 template <int HD> size_t decode_tma_smem() {
@@ -624,8 +629,8 @@ __device__ __forceinline__ void piece_at(Piece& pc, long long pos, long long sha
   if (pc.row0 >= t.rows_total) return;
   const int qi_lo = pc.row0 / t.G, qi_hi = min(t.q_len - 1, (pc.row0 + 15) / t.G);
   const int hi_key = t.pos0 + qi_hi;
-  pc.lo_key = window > 0 ? max(0, t.pos0 + qi_lo - window + 1) : 0;
-  const int lo_entry = window > 0 ? max(0, t.pos0 - window + 1) : 0;      // the request's tiles start here
+  pc.lo_key = bspec::mask_lo(t.pos0 + qi_lo, window);
+  const int lo_entry = bspec::mask_lo(t.pos0, window);      // the request's tiles start here
   const int lo_al = (lo_entry / KT) * KT;
   pc.k_begin = lo_al + t0 * KT;
   pc.k_end = min(hi_key + 1, lo_al + t1 * KT);
@@ -647,7 +652,7 @@ __device__ __forceinline__ bool make_shares(Shares& sh, int* cum, int* pos0_of, 
     int tiles = 0, pos0 = 0;
     if (ql > 0 && ql <= max_q_short) {
       pos0 = kv_len != nullptr ? len_after - ql : positions[qb];
-      const int lo_entry = window > 0 ? max(0, pos0 - window + 1) : 0;
+      const int lo_entry = bspec::mask_lo(pos0, window);
       tiles = (pos0 + ql - (lo_entry / KT) * KT + KT - 1) / KT;
     }
     pos0_of[e] = pos0;
@@ -701,7 +706,8 @@ __device__ __forceinline__ bool make_shares(Shares& sh, int* cum, int* pos0_of, 
 template <int HD>
 __device__ __forceinline__ void join_parts(float* Wt, __nv_bfloat16* __restrict__ out, const float* __restrict__ o_part,
                                            const float* __restrict__ ml_part, int e, int g, int row0, int q_begin,
-                                           int rows_total, int G, int Hq, int n_parts, int max_parts, int rows_pe) {
+                                           int rows_total, int G, int Hq, int n_parts, int max_parts, int rows_pe,
+                                           const float* __restrict__ sink_l2) {
   const int nrows = min(16, rows_total - row0);
   float* Inv = Wt + 64 * 16;
   {
@@ -733,6 +739,7 @@ __device__ __forceinline__ void join_parts(float* Wt, __nv_bfloat16* __restrict_
     }
 #pragma unroll
     for (int o = 1; o < 8; o <<= 1) lt += __shfl_xor_sync(0xffffffffu, lt, o);
+    lt = bspec::with_sink(lt, mt, sink_l2, h);
     if (live && j8 == 0) Inv[row] = lt > 0.f ? 1.f / lt : 0.f;
   }
   bar_consumers();
@@ -775,7 +782,8 @@ attn_decode_shares_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv
                           const int* __restrict__ kv_len,
                           const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, int n_entries, int Hq,
                           int Hkv, int page_size, float scale_log2, int window, int max_parts, int rows_pe,
-                          int row_tiles, int max_q_short) {
+                          int row_tiles, int max_q_short,
+                    const float* __restrict__ sink_l2) {
   // Lengths, positions and block tables were uploaded before the step's first kernel, and every cached key below
   // the first new token was written by earlier steps: all of that may be read, and those tiles fetched, while the
   // kernel before this one (which writes q and the new tokens' keys and values) still runs.
@@ -890,7 +898,7 @@ attn_decode_shares_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv
         const int row = pc.row0 + (lane >> 2) + 8 * r;
         const int qi = row / t.G;
         lim[r] = row < t.rows_total ? t.pos0 + qi : -1;
-        lo[r] = window > 0 ? max(0, t.pos0 + qi - window + 1) : 0;
+        lo[r] = bspec::mask_lo(t.pos0 + qi, window);
       }
       load_q_tile<HD>(Qs, q, q_row_stride, t, pc.row0, 16);
       bar_consumers();
@@ -986,7 +994,8 @@ attn_decode_shares_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv
       const float lt = Fs[64 + row];
       const int r = pc.row0 + row, qi = r / t.G, h = pc.g * t.G + (r - qi * t.G);
       if (pc.n_parts == 1) {
-        const float inv = lt > 0.f ? 1.f / lt : 0.f;
+        const float ls = bspec::with_sink(lt, Fs[80 + row], sink_l2, h);
+        const float inv = ls > 0.f ? 1.f / ls : 0.f;
         uint2 packed;
         packed.x = pack_bf16(acc.x * inv, acc.y * inv);
         packed.y = pack_bf16(acc.z * inv, acc.w * inv);
@@ -1024,7 +1033,7 @@ attn_decode_shares_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv
     __threadfence();
     const int e = pend_e[i], q_begin = rows_of[e] & ((1 << 26) - 1), q_len = rows_of[e] >> 26, G = Hq / Hkv;
     join_parts<HD>(Wt, out, o_part, ml_part, e, pend_g[i], pend_rt[i] * 16, q_begin, q_len * G, G, Hq, pend_parts[i],
-                   max_parts, rows_pe);
+                   max_parts, rows_pe, sink_l2);
   }
 }
 
@@ -1129,7 +1138,8 @@ attn_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_b
                         long long q_row_stride, __nv_bfloat16* __restrict__ out, int* __restrict__ status,
                         const int* __restrict__ qo_indptr, const int* __restrict__ positions,
                         const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, int Hq, int Hkv,
-                        int page_size, float scale_log2, int window, int min_q_long) {
+                        int page_size, float scale_log2, int window, int min_q_long,
+                    const float* __restrict__ sink_l2) {
   bspec::pdl_prologue(9);
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -1150,7 +1160,7 @@ attn_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_b
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qi_lo = row0 / t.G, qi_hi = min(t.q_len - 1, (row0 + PREFILL_ROWS - 1) / t.G);
   const int hi_key = t.pos0 + qi_hi;
-  const int lo_key = window > 0 ? max(0, t.pos0 + qi_lo - window + 1) : 0;
+  const int lo_key = bspec::mask_lo(t.pos0 + qi_lo, window);
   const int k_begin = (lo_key / KT) * KT, k_end = hi_key + 1;
   const int n_tiles = (k_end - k_begin + KT - 1) / KT;
   const int* table = kv_indices + kv_indptr[e];
@@ -1202,12 +1212,12 @@ attn_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_b
     const int row = wrow0 + (lane >> 2) + 8 * r;
     const int qi = row / t.G;
     lim[r] = row < t.rows_total ? t.pos0 + qi : -1;
-    lo[r] = window > 0 ? max(0, t.pos0 + qi - window + 1) : 0;
+    lo[r] = bspec::mask_lo(t.pos0 + qi, window);
   }
   const bool warp_live = wrow0 < t.rows_total;
   const int warp_hi = t.pos0 + min(t.q_len - 1, (wrow0 + 15) / t.G);          // last key any row of the warp sees
   const int warp_full = t.pos0 + wrow0 / t.G;                                 // keys <= this are seen by all its rows
-  const int warp_lo = window > 0 ? t.pos0 + min(t.q_len - 1, (wrow0 + 15) / t.G) - window + 1 : 0;
+  const int warp_lo = bspec::mask_lo(t.pos0 + min(t.q_len - 1, (wrow0 + 15) / t.G), window);
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   float o[HD / 8][4];
 #pragma unroll
@@ -1262,7 +1272,8 @@ attn_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_b
     const int row = wrow0 + (lane >> 2) + 8 * r;
     if (row >= t.rows_total) continue;
     const int qi = row / t.G, h = g * t.G + (row - qi * t.G);
-    const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+    const float ls = bspec::with_sink(l[r], m[r], sink_l2, h);
+    const float inv = ls > 0.f ? 1.f / ls : 0.f;
     __nv_bfloat16* op = out + ((size_t)(t.q_begin + qi) * Hq + h) * HD;
 #pragma unroll
     for (int nd = 0; nd < HD / 8; ++nd) {
@@ -1283,7 +1294,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
                     const __nv_bfloat16* __restrict__ cache, const int* __restrict__ qo_indptr,
                     const int* __restrict__ positions, const int* __restrict__ kv_indptr,
                     const int* __restrict__ kv_indices, int Hq, int Hkv, int page_size, float scale_log2, int window,
-                    int min_q_long, long long n_pages) {
+                    int min_q_long, long long n_pages,
+                    const float* __restrict__ sink_l2) {
   bspec::pdl_prologue(9);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [64][HD]
@@ -1299,7 +1311,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qi_lo = row0 / t.G, qi_hi = min(t.q_len - 1, (row0 + 63) / t.G);
   const int hi_key = t.pos0 + qi_hi;
-  const int lo_key = window > 0 ? max(0, t.pos0 + qi_lo - window + 1) : 0;
+  const int lo_key = bspec::mask_lo(t.pos0 + qi_lo, window);
   const int k_begin = (lo_key / KT) * KT, k_end = hi_key + 1;
   const int* table = kv_indices + kv_indptr[e];
   const int wrow0 = row0 + 16 * warp;
@@ -1309,7 +1321,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
     const int row = wrow0 + (lane >> 2) + 8 * r;
     const int qi = row / t.G;
     lim[r] = row < t.rows_total ? t.pos0 + qi : -1;
-    lo[r] = window > 0 ? max(0, t.pos0 + qi - window + 1) : 0;
+    lo[r] = bspec::mask_lo(t.pos0 + qi, window);
   }
   // keys this warp's rows can see at all (skip tiles beyond its own last row)
   const int warp_hi = t.pos0 + min(t.q_len - 1, (wrow0 + 15) / t.G);
@@ -1364,7 +1376,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
     const int row = wrow0 + (lane >> 2) + 8 * r;
     if (row >= t.rows_total) continue;
     const int qi = row / t.G, h = g * t.G + (row - qi * t.G);
-    const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+    const float ls = bspec::with_sink(l[r], m[r], sink_l2, h);
+    const float inv = ls > 0.f ? 1.f / ls : 0.f;
     __nv_bfloat16* op = out + ((size_t)(t.q_begin + qi) * Hq + h) * HD;
 #pragma unroll
     for (int nd = 0; nd < HD / 8; ++nd) {
@@ -1386,7 +1399,7 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
            const int* kv_indptr, const int* kv_indices, int n_entries, int n_tokens, int max_q_len, int Hq, int Hkv,
            int page_size, float scale, int window, int n_splits, int max_q_short, int run_decode, int run_prefill,
            cudaStream_t stream, int balanced = 0, const int* kv_len = nullptr,
-           long long check_pages = 0x7fffffffffffll) {
+           long long check_pages = 0x7fffffffffffll, const float* sink_l2 = nullptr) {
   const float scale_log2 = scale * 1.4426950408889634f;
   const int G = Hq / Hkv;
   // The opt-in to large shared memory and the resident-CTA count are facts of a device: set up once per device,
@@ -1424,21 +1437,22 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
         BSPEC_LAUNCH((attn_decode_shares_kernel<HD>), dim3(resident), DECODE_TMA_THREADS, decode_shares_smem<HD>(),
                      stream, kv_map, q, q_row_stride, out, o_part, ml_part, tile_counters, status, qo_indptr, positions,
                      kv_len, kv_indptr, kv_indices, n_entries, Hq, Hkv, page_size, scale_log2, window, n_splits,
-                     short_q, row_tiles, max_q_short);
+                     short_q, row_tiles, max_q_short, sink_l2);
         launched = true;
        }
       }
       if (!launched && make_map_2d_bf16(&kv_map, cache, kv_rows, HD, page_size, 64)) {
         BSPEC_LAUNCH((attn_decode_tma_kernel<HD>), grid, DECODE_TMA_THREADS, decode_tma_smem<HD>(), stream, kv_map, q,
                      q_row_stride, out, o_part, ml_part, tile_counters, status, qo_indptr, positions, kv_indptr,
-                     kv_indices, Hq, Hkv, page_size, scale_log2, window, n_splits, row_tiles, max_q_short);
+                     kv_indices, Hq, Hkv, page_size, scale_log2, window, n_splits, row_tiles, max_q_short, sink_l2);
         launched = true;
       }
     }
     if (!launched)
       BSPEC_LAUNCH((attn_decode_kernel<HD>), grid, NTHREADS, decode_smem<HD>(), stream,
                    q, q_row_stride, out, o_part, ml_part, tile_counters, cache, qo_indptr, positions, kv_indptr,
-                   kv_indices, Hq, Hkv, page_size, scale_log2, window, n_splits, row_tiles, max_q_short, check_pages);
+                   kv_indices, Hq, Hkv, page_size, scale_log2, window, n_splits, row_tiles, max_q_short, check_pages,
+                   sink_l2);
     const int err = (int)cudaGetLastError();
     if (err) return err;
   }
@@ -1452,7 +1466,7 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
         dim3 grid((max_q_len * G + PREFILL_ROWS - 1) / PREFILL_ROWS, Hkv, n_entries);
         BSPEC_LAUNCH((attn_prefill_tma_kernel<HD>), grid, PREFILL_TMA_THREADS, prefill_tma_smem<HD>(), stream, kv_map,
                      q, q_row_stride, out, status, qo_indptr, positions, kv_indptr, kv_indices, Hq, Hkv, page_size,
-                     scale_log2, window, max_q_short + 1);
+                     scale_log2, window, max_q_short + 1, sink_l2);
         launched = true;
       }
      }
@@ -1461,7 +1475,7 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
       dim3 grid((max_q_len * G + 63) / 64, Hkv, n_entries);
       BSPEC_LAUNCH((attn_prefill_kernel<HD>), grid, NTHREADS, prefill_smem<HD>(), stream,
                    q, q_row_stride, out, cache, qo_indptr, positions, kv_indptr, kv_indices, Hq, Hkv, page_size,
-                   scale_log2, window, max_q_short + 1, check_pages);
+                   scale_log2, window, max_q_short + 1, check_pages, sink_l2);
     }
     return (int)cudaGetLastError();
   }
@@ -1482,19 +1496,44 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
 // n_splits * hd], ml_part likewise).  kv_len (may be null): [n_entries] each request's length after this step, which saves
 // those kernels the dependent load of positions[qo_indptr[e]].  pages_in_all: pages of the cache layer whether or
 // not n_pages is given (the checked build compares the page ids that the plain-copy kernels read with it; 0: unknown).
+BSPEC_API int bspec_attention_bf16_masked(const void* q, long long q_row_stride, void* out, float* o_part, float* ml_part,
+                                          int* tile_counters, int* status, long long n_pages, const void* cache,
+                                          const int* qo_indptr, const int* positions, const int* tok_entry,
+                                          const int* kv_indptr, const int* kv_indices, int n_entries, int n_tokens,
+                                          int max_q_len, int Hq, int Hkv, int hd, int page_size, float scale, int window,
+                                          int n_splits, int max_q_short, int run_decode, int run_prefill, int balanced,
+                                          const int* kv_len, long long pages_in_all, const float* sink_l2,
+                                          cudaStream_t stream);
 BSPEC_API int bspec_attention_bf16(const void* q, long long q_row_stride, void* out, float* o_part, float* ml_part,
                                    int* tile_counters, int* status, long long n_pages, const void* cache, const int* qo_indptr, const int* positions,
                                    const int* tok_entry, const int* kv_indptr, const int* kv_indices, int n_entries,
                                    int n_tokens, int max_q_len, int Hq, int Hkv, int hd, int page_size, float scale,
                                    int window, int n_splits, int max_q_short, int run_decode, int run_prefill,
                                    int balanced, const int* kv_len, long long pages_in_all, cudaStream_t stream) {
+  return bspec_attention_bf16_masked(q, q_row_stride, out, o_part, ml_part, tile_counters, status, n_pages, cache,
+                                     qo_indptr, positions, tok_entry, kv_indptr, kv_indices, n_entries, n_tokens,
+                                     max_q_len, Hq, Hkv, hd, page_size, scale, window, n_splits, max_q_short, run_decode,
+                                     run_prefill, balanced, kv_len, pages_in_all, nullptr, stream);
+}
+
+// The same with the other masks and a sink.  ``window`` < 0: a chunk mask of -window positions (a query sees the
+// keys of its own chunk).  ``sink_l2`` (may be null): float32 per query head, the sink times log2(e); it joins the
+// softmax denominator as exp(sink).
+BSPEC_API int bspec_attention_bf16_masked(const void* q, long long q_row_stride, void* out, float* o_part, float* ml_part,
+                                          int* tile_counters, int* status, long long n_pages, const void* cache,
+                                          const int* qo_indptr, const int* positions, const int* tok_entry,
+                                          const int* kv_indptr, const int* kv_indices, int n_entries, int n_tokens,
+                                          int max_q_len, int Hq, int Hkv, int hd, int page_size, float scale, int window,
+                                          int n_splits, int max_q_short, int run_decode, int run_prefill, int balanced,
+                                          const int* kv_len, long long pages_in_all, const float* sink_l2,
+                                          cudaStream_t stream) {
   if (n_entries <= 0 || n_tokens <= 0) return 0;
   if (Hq % Hkv != 0 || n_splits < 1 || n_splits > 64) return (int)cudaErrorInvalidValue;
 #define GO(HDV)                                                                                                    \
   return launch<HDV>((const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, o_part, ml_part, tile_counters,   \
                      status, n_pages * 2 * Hkv * page_size, (const __nv_bfloat16*)cache, qo_indptr, positions, tok_entry, kv_indptr, kv_indices, n_entries, \
                      n_tokens, max_q_len, Hq, Hkv, page_size, scale, window, n_splits, max_q_short, run_decode,      \
-                     run_prefill, stream, balanced, kv_len, pages_in_all > 0 ? pages_in_all : 0x7fffffffffffll)
+                     run_prefill, stream, balanced, kv_len, pages_in_all > 0 ? pages_in_all : 0x7fffffffffffll, sink_l2)
   if (hd == 64) GO(64);
   if (hd == 128) GO(128);
   if (hd == 256) GO(256);

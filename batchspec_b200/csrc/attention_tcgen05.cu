@@ -176,7 +176,7 @@ __device__ __forceinline__ bool load_item(Item& it, int idx, int Hq, int Hkv, in
   it.g = g;
   it.row0 = (n_cta_tiles - 1 - z) * QT * ROWS;
   const int qi_lo = it.row0 / t.G;
-  it.lo_key = window > 0 ? max(0, t.pos0 + qi_lo - window + 1) : 0;
+  it.lo_key = bspec::mask_lo(t.pos0 + qi_lo, window);
   it.k_begin = (it.lo_key / KT) * KT;
 #pragma unroll
   for (int tt = 0; tt < QT; ++tt) {
@@ -220,7 +220,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
                        int* __restrict__ status, const int* __restrict__ qo_indptr, const int* __restrict__ positions,
                        const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, int Hq, int Hkv,
                        int n_entries, int n_items, int page_size, float scale_log2, int window, int min_q_long,
-                       int q_by_tma, int* __restrict__ work) {
+                       int q_by_tma, int* __restrict__ work, const float* __restrict__ sink_l2) {
   // The step's lengths, positions and block tables were uploaded before its first kernel: the set-up below and the
   // look-up of the CTA's first item read nothing that the kernel before this one writes, so they run under its
   // tail; q, the new tokens' keys and `out` are touched only after the wait.
@@ -473,7 +473,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
       const int qi = live ? r / t.G : 0;
       const int h = g * t.G + (live ? r - qi * t.G : 0);
       const int lim = live ? t.pos0 + qi : -1;
-      const int lo = window > 0 ? max(0, t.pos0 + qi - window + 1) : 0;
+      const int lo = bspec::mask_lo(t.pos0 + qi, window);
       const int my_k_end = it.k_end_t[tt];
       if (!q_by_tma) {
         // Q tile: this thread copies its own row (16 chunks of 16 bytes) into the swizzled operand layout.  The
@@ -607,7 +607,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
         // O: tensor memory -> registers (normalised, bfloat16) -> this warp's own 32 rows of a staging tile in
         // shared memory -> global memory in runs of 128 bytes, 8 lanes per row, 64 columns at a time.  A thread
         // storing its own row would touch 32 different lines per instruction.
-        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const float l_all = bspec::with_sink(l, m_ref, sink_l2, h);          // the sink's term, if there is one
+        const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
         const unsigned char* wbase = reinterpret_cast<const unsigned char*>(Os + tt * SUBQ) + (quad * 32) * 128;
         const int sub = lane >> 3, ch8 = lane & 7;                   // four rows per pass, 8 chunks of a half row
         const int r_warp = it.row0 + tt * ROWS + quad * 32;
@@ -690,12 +691,31 @@ bool make_q_map(CUtensorMap* map, const void* q, long long q_row_stride, int Hq,
 // serves them).  head_dim must be 128 and page_size one of 8 / 16 / 32 / 64; n_pages: pages of this cache layer;
 // n_tokens: rows of q; work: two ints on the device, zero before the first launch and left zero by every launch
 // that runs to its end.  Returns cudaErrorInvalidValue for what it cannot do, so the caller can fall back.
+BSPEC_API int bspec_attention_prefill_tc_masked(const void* q, long long q_row_stride, void* out, int* status,
+                                                long long n_pages, const void* cache, const int* qo_indptr,
+                                                const int* positions, const int* kv_indptr, const int* kv_indices,
+                                                int n_entries, long long n_tokens, int max_q_len, int Hq, int Hkv,
+                                                int hd, int page_size, float scale, int window, int min_q_long,
+                                                int* work, const float* sink_l2, cudaStream_t stream);
 BSPEC_API int bspec_attention_prefill_tc(const void* q, long long q_row_stride, void* out, int* status,
                                          long long n_pages, const void* cache, const int* qo_indptr,
                                          const int* positions, const int* kv_indptr, const int* kv_indices,
                                          int n_entries, long long n_tokens, int max_q_len, int Hq, int Hkv, int hd,
                                          int page_size, float scale, int window, int min_q_long, int* work,
                                          cudaStream_t stream) {
+  return bspec_attention_prefill_tc_masked(q, q_row_stride, out, status, n_pages, cache, qo_indptr, positions, kv_indptr,
+                                           kv_indices, n_entries, n_tokens, max_q_len, Hq, Hkv, hd, page_size, scale,
+                                           window, min_q_long, work, nullptr, stream);
+}
+
+// The same with the other masks and a sink: ``window`` < 0 is a chunk mask of -window positions, ``sink_l2`` (may be
+// null) one float32 per query head, the sink times log2(e).
+BSPEC_API int bspec_attention_prefill_tc_masked(const void* q, long long q_row_stride, void* out, int* status,
+                                                long long n_pages, const void* cache, const int* qo_indptr,
+                                                const int* positions, const int* kv_indptr, const int* kv_indices,
+                                                int n_entries, long long n_tokens, int max_q_len, int Hq, int Hkv,
+                                                int hd, int page_size, float scale, int window, int min_q_long,
+                                                int* work, const float* sink_l2, cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return 0;
   if (hd != HD || Hq % Hkv != 0 || page_size % 8 != 0 || KT % page_size != 0 || status == nullptr || n_pages <= 0 ||
       n_tokens <= 0 || work == nullptr)
@@ -723,7 +743,7 @@ BSPEC_API int bspec_attention_prefill_tc(const void* q, long long q_row_stride, 
   BSPEC_LAUNCH((attn_prefill_tc_kernel), dim3(grid), THREADS, smem_bytes(), stream, kv_map, q_map,
                (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, status, qo_indptr, positions, kv_indptr,
                kv_indices, Hq, Hkv, n_entries, (int)n_items, page_size, scale * 1.4426950408889634f, window, min_q_long,
-               q_by_tma, work);
+               q_by_tma, work, sink_l2);
   return BSPEC_LAUNCH_CHECK();
 }
 

@@ -38,6 +38,17 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// First key that a query at position ``pos`` may see besides causality.  ``window`` > 0: the last ``window`` keys;
+// ``window`` < 0: the keys of the query's own chunk of -window positions (chunks counted from position 0); 0: all.
+__device__ __forceinline__ int mask_lo(int pos, int window) {
+  return window > 0 ? max(0, pos - window + 1) : (window < 0 ? (pos / -window) * -window : 0);
+}
+// A softmax sink joins the denominator as exp(sink) and has no value.  With the running maximum ``m`` and sum ``l``
+// in base-2 units and ``sink_l2`` = sink * log2(e) per query head (null: none): the sum with the sink's term.
+__device__ __forceinline__ float with_sink(float l, float m, const float* __restrict__ sink_l2, int h) {
+  return sink_l2 != nullptr && l > 0.f ? l + exp2f(sink_l2[h] - m) : l;
+}
+
 // Block-wide sum with a fixed reduction tree (same order whatever else runs).
 // `scratch` holds at least 32 floats of shared memory.  All threads get the sum.
 __device__ __forceinline__ float block_sum(float v, float* scratch) {

@@ -101,6 +101,13 @@ _SIGNATURES = {
     "bspec_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                              c_int, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p],
+    "bspec_attention_bf16_masked": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
+                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                    c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                    c_longlong, c_void_p, c_void_p],
+    "bspec_attention_prefill_tc_masked": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
+                                          c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int,
+                                          c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "bspec_gemm_tc_plan": [c_int, c_int, c_int, c_int, c_void_p],
     "bspec_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     "bspec_gemm_tc_clamped_glu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p, c_int,
@@ -537,15 +544,28 @@ def _attention_plan(device, ctx, tables, n_heads: int, n_kv_heads: int, head_dim
             _ptr(getattr(ctx, "kv_len", None)))
 
 
+def sink_table(sink: torch.Tensor) -> torch.Tensor:
+    """The form in which the tensor-core attention kernels take softmax sinks: float32, times log2(e)."""
+    return (sink.to(torch.float32) * 1.4426950408889634).contiguous()
+
+
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, ctx, tables, n_heads: int,
-                    n_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
+                    n_kv_heads: int, head_dim: int, scale: float, window: int = 0, chunk: int = 0,
+                    sink: Optional[torch.Tensor] = None, sink_l2: Optional[torch.Tensor] = None) -> None:
     """Causal attention of the step's tokens over their requests' cached keys.
     ``qkv``: [n, >= n_heads*head_dim] rows with the (already rotated) query heads
     first.  ``ctx`` gives qo_indptr / positions / n_entries / max_q_len, ``tables``
     the block tables of the cache group.  bfloat16 with head_dim 64/128/256 runs
-    on the tensor-core kernels; everything else on the generic float32-math kernel."""
-    _require_cuda(qkv, out, cache)
+    on the tensor-core kernels; everything else on the generic float32-math kernel.
+    ``window`` > 0 keeps the last ``window`` keys, ``chunk`` > 0 the keys of the query's own chunk of ``chunk``
+    positions (one of the two at most).  ``sink`` (float32 per query head, with ``sink_l2`` its ``sink_table``) adds
+    exp(sink) to the softmax denominator."""
+    _require_cuda(qkv, out, cache, sink, sink_l2)
     assert qkv.stride(1) == 1 and out.is_contiguous() and out.dtype == qkv.dtype == cache.dtype
+    assert not (window and chunk) and window >= 0 and chunk >= 0
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == n_heads and sink_l2 is not None
+                            and sink_l2.dtype == torch.float32 and sink_l2.numel() == n_heads)
+    mask = int(window) if window else -int(chunk)      # the kernels take a chunk mask as a negative window
     lib = load_library()
     if qkv.dtype == torch.bfloat16 and head_dim in (64, 128, 256) and not FORCE_GENERIC_ATTENTION:
         # Everything that depends on the step and the layer's sizes only is worked out once per step (all layers of
@@ -558,28 +578,29 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
          tok_entry, kv_indptr, kv_indices, kv_len) = plan
         if prefill_tc:
             # long portions on the tcgen05 kernel; what is left for the call below are the short requests
-            _check(lib.bspec_attention_prefill_tc(
+            _check(lib.bspec_attention_prefill_tc_masked(
                 qkv.data_ptr(), qkv.stride(0), out.data_ptr(), status, cache.shape[0], cache.data_ptr(), qo, pos,
                 kv_indptr, kv_indices, ctx.n_entries, qkv.shape[0], ctx.max_q_len, n_heads, n_kv_heads, head_dim,
                 tables.page_size,
-                float(scale), int(window), short + 1, _work_counter(qkv.device).data_ptr(), _stream()),
+                float(scale), mask, short + 1, _work_counter(qkv.device).data_ptr(), _ptr(sink_l2), _stream()),
                 "attention_prefill_tc")
             run_prefill = 0
             if not run_decode:
                 return
-        _check(lib.bspec_attention_bf16(
+        _check(lib.bspec_attention_bf16_masked(
             qkv.data_ptr(), qkv.stride(0), out.data_ptr(), o_part, ml_part, counters, status,
             cache.shape[0] if tma else 0, cache.data_ptr(), qo, pos, tok_entry, kv_indptr, kv_indices, ctx.n_entries,
-            ctx.n_tokens, ctx.max_q_len, n_heads, n_kv_heads, head_dim, tables.page_size, float(scale), int(window),
-            n_splits, short, run_decode, run_prefill, balanced, kv_len, cache.shape[0], _stream()), "attention_bf16")
+            ctx.n_tokens, ctx.max_q_len, n_heads, n_kv_heads, head_dim, tables.page_size, float(scale), mask,
+            n_splits, short, run_decode, run_prefill, balanced, kv_len, cache.shape[0], _ptr(sink_l2), _stream()),
+            "attention_bf16")
         global _launches
         _launches += 1 if run_decode and run_prefill else 0
         return
-    _check(lib.bspec_attention_generic(
+    _check(lib.bspec_attention_masked(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), cache.data_ptr(), _dtype_code(qkv.dtype),
         ctx.qo_indptr.data_ptr(), ctx.positions.data_ptr(), tables.kv_indptr.data_ptr(), tables.kv_indices.data_ptr(),
-        ctx.n_entries, ctx.max_q_len, n_heads, n_kv_heads, head_dim, tables.page_size, float(scale), int(window),
-        cache.shape[0], _stream()), "attention_generic")
+        ctx.n_entries, ctx.max_q_len, n_heads, n_kv_heads, head_dim, head_dim, tables.page_size, float(scale),
+        int(window), int(chunk), _ptr(sink), cache.shape[0], _stream()), "attention_generic")
 
 
 def qkv_prepare(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, v_dim: int,

@@ -140,8 +140,11 @@ class DecoderModel:
                 ops.residual_update(resid, pending, scale, first)
                 pending, scale = None, 1.0
             block = self.blocks[run.layer]
-            resid, pending = block.forward(resid, pending, ctx, self.caches[e], scale)
-            scale = block.residual_mult
+            # a block whose forward knows no branch factors (one registered from outside) can follow any block that
+            # leaves its branch unscaled
+            extra = {} if scale == 1.0 else {"pending_scale": scale}
+            resid, pending = block.forward(resid, pending, ctx, self.caches[e], **extra)
+            scale = getattr(block, "residual_mult", 1.0)
             if self.layer_probe is not None:
                 after = resid.clone()
                 ops.residual_update(after, pending, scale)

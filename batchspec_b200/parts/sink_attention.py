@@ -46,7 +46,7 @@ class SinkAttention(Mixer):
         if self.chunk < 0 or self.window < 0 or (self.chunk and self.window):
             raise ValueError("give a chunk size or a window, both positive, not both")
         self.position = build_part(POSITION_ENCODINGS, position, runtime)
-        self.wqkv = self.wo = self.b = self.sinks = None
+        self.wqkv = self.wo = self.b = self.sinks = self.sinks_l2 = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         q, k, v = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim, self.n_kv_heads * self.v_dim
@@ -66,6 +66,7 @@ class SinkAttention(Mixer):
             self.b = torch.cat([params[n].to(torch.float32) for n in ("q_bias", "k_bias", "v_bias")]).contiguous()
         if self.sink:
             self.sinks = params["sink"].to(torch.float32).contiguous()
+            self.sinks_l2 = ops.sink_table(self.sinks)
 
     def cache_spec(self) -> CacheSpec:
         policy = "chunk" if self.chunk else ("window" if self.window else "full")
@@ -88,7 +89,13 @@ class SinkAttention(Mixer):
                                 tables.kv_indptr, tables.kv_indices, cache.kv, tables.page_size, write_kv=cache.owner)
         out = torch.empty((n, H * vd), dtype=x.dtype, device=x.device)
         with bucket("attn.compute"):
-            ops.masked_attention(q, out, cache.kv, ctx, tables, H, G, hd, vd, self.scale, self.window, self.chunk,
-                                 self.sinks)
+            if vd == hd:
+                # values as wide as keys: the plain attention part's kernels (tensor cores for bfloat16 heads of
+                # 64, 128 or 256), which take the chunk mask and the sink too
+                ops.paged_attention(q, out, cache.kv, ctx, tables, H, G, hd, self.scale, self.window, self.chunk,
+                                    self.sinks, self.sinks_l2)
+            else:
+                ops.masked_attention(q, out, cache.kv, ctx, tables, H, G, hd, vd, self.scale, self.window, self.chunk,
+                                     self.sinks)
         with bucket("attn.o_proj"):
             return ops.linear(out, self.wo)
