@@ -391,10 +391,145 @@ def latent_attention_alone(z, pk, iters=20):
     return out
 
 
+LUPUSUN_SIZES = {
+    # width, attention heads / kv heads, head size, chunk of the mask, delta rule heads / q-k heads, feed-forward
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, chunk=1024, delta_heads=16, delta_kv_heads=8, dense_ff=8448),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, chunk=1024, delta_heads=32, delta_kv_heads=16, dense_ff=14336),
+}
+
+
+def lupusun_config_json(z, layers, vocab=32000):
+    """Attention and delta rule layers in turn, each with a feed-forward; no loop, so that the depth equals the
+    Llama model's."""
+    att = dict(type="attention", mlp=dict(kind="dense", ff=z["dense_ff"]),
+               mixer=dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5,
+                          mask=dict(size=z["chunk"]),
+                          rot=dict(base=500000.0, dims=z["dim"], scaling=dict(factor=8.0, original=8192, fast=32.0, slow=1.0))))
+    dlt = dict(type="delta", mlp=dict(kind="dense", ff=z["dense_ff"]),
+               mixer=dict(heads=z["delta_heads"], kv_heads=z["delta_kv_heads"], dim=z["dim"], vdim=z["dim"], conv=4))
+    return dict(architecture="Lupusun", vocab=vocab, width=z["width"], norm=dict(eps=1e-5), residual_mult=0.7,
+                layers=[att if i % 2 == 0 else dlt for i in range(layers)])
+
+
+def _time(run, iters=20):
+    import torch
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        run()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / iters
+
+
+def lupusun_kernels_alone(z, pk, iters=20):
+    """The design's own kernels by themselves, each beside the like kernel of the Llama model at equal sizes:
+    attention with the chunk mask and the sink against plain causal attention (a prompt of 4,096 tokens: FLOP/s over
+    the visible pairs against the measured product peak; a decode step of 64 requests x 4,096 keys: bytes of visible
+    keys and values against the measured copy rate), the q/k/v preparation against the rotate-and-append kernel
+    (bytes), and the delta rule's kernels (bytes of state read and written for decode; FLOP/s for a prompt)."""
+    import torch
+    from types import SimpleNamespace
+    from batchspec_b200.kernels import ops
+    dev = "cuda:0"
+    Hq, G, hd, ps, chunk = z["heads"], z["kv_heads"], z["dim"], 16, z["chunk"]
+    out = {}
+    sink = torch.linspace(-1.0, 1.0, Hq, device=dev)
+    sink_l2 = ops.sink_table(sink)
+
+    def step_ctx(q_lens, ctx_len):
+        n, B = sum(q_lens), len(q_lens)
+        pages_per = -(-ctx_len // ps)
+        qo = torch.tensor([0] + list(__import__("itertools").accumulate(q_lens)), dtype=torch.int32, device=dev)
+        pos = torch.cat([torch.arange(ctx_len - q, ctx_len) for q in q_lens]).to(dev, torch.int32)
+        ent = torch.cat([torch.full((q,), i) for i, q in enumerate(q_lens)]).to(dev, torch.int32)
+        ctx = SimpleNamespace(qo_indptr=qo, positions=pos, tok_entry=ent, n_entries=B, n_tokens=n, max_q_len=max(q_lens),
+                              max_kv_len=ctx_len, kv_len=torch.full((B,), ctx_len, dtype=torch.int32, device=dev),
+                              state_slots=torch.arange(B, dtype=torch.int32, device=dev),
+                              extras={"min_q_len": min(q_lens)})
+        tables = SimpleNamespace(kv_indptr=torch.arange(B + 1, dtype=torch.int32, device=dev) * pages_per,
+                                 kv_indices=torch.randperm(B * pages_per, device=dev).to(torch.int32), page_size=ps)
+        return ctx, tables, n, B, pages_per
+
+    for name, q_lens, ctx_len in (("prompt_4096", [4096], 4096), ("decode_64x4096", [1] * 64, 4096)):
+        ctx, tables, n, B, pages_per = step_ctx(q_lens, ctx_len)
+        cache = torch.randn(B * pages_per, 2, ps * G * hd, device=dev).bfloat16()
+        q = torch.randn(n, Hq * hd, device=dev).bfloat16()
+        o = torch.empty(n, Hq * hd, device=dev, dtype=torch.bfloat16)
+        for label, ck, sk, sk2 in (("chunk_sink", chunk, sink, sink_l2), ("causal", 0, None, None)):
+            ctx.extras = {"min_q_len": min(q_lens)}
+            ms = _time(lambda: ops.paged_attention(q, o, cache, ctx, tables, Hq, G, hd, hd ** -0.5, 0, ck, sk, sk2), iters)
+            span = ck or (1 << 30)
+            pairs = sum(p - (p // span) * span + 1 for p in range(ctx_len - q_lens[0], ctx_len)) * len(q_lens)
+            if name.startswith("prompt"):
+                flops = 4.0 * Hq * hd * pairs
+                out[f"attention_{name}_{label}"] = dict(ms=round(ms, 4), tflops=round(flops / ms / 1e9, 1),
+                                                        frac_of_measured=round(flops / ms / 1e9 / pk["bf16_tflops"], 4))
+            else:
+                nbytes = pairs * 2 * G * hd * 2
+                out[f"attention_{name}_{label}"] = dict(ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1),
+                                                        frac_of_measured=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
+    # q/k/v preparation against rotate-and-append: bytes read and written per token
+    ctx, tables, n, B, pages_per = step_ctx([4096], 4096)
+    cache = torch.zeros(pages_per, 2, ps * G * hd, device=dev, dtype=torch.bfloat16)
+    width = (Hq + 2 * G) * hd
+    qkv32 = torch.randn(n, width, device=dev)
+    qkv16 = torch.randn(n, width, device=dev).bfloat16()
+    bias = torch.randn(width, device=dev)
+    freq = ops.rope_frequency_table(torch.pow(torch.tensor(500000.0, dtype=torch.float64), -torch.arange(0, hd // 2, dtype=torch.float64) * 2 / hd), dev)
+    ms = _time(lambda: ops.qkv_prepare(qkv32, Hq, G, hd, hd, bias, freq, hd, False, 1.2, 1e-5, ctx.positions, ctx.tok_entry,
+                                       tables.kv_indptr, tables.kv_indices, cache, ps), iters)
+    nbytes = n * width * (4 + 2)
+    out["qkv_prepare_4096"] = dict(ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1), frac_of_measured=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
+    ms = _time(lambda: ops.rope_kv_append(qkv16, Hq, G, hd, freq, hd, False, ctx.positions, ctx.tok_entry, tables.kv_indptr,
+                                          tables.kv_indices, cache, ps), iters)
+    nbytes = n * (width * 2 + Hq * hd * 2 + 2 * G * hd * 2)
+    out["rope_kv_append_4096"] = dict(ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1), frac_of_measured=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
+    # the delta rule's kernels
+    Hd, Gd, dk, dv, taps = z["delta_heads"], z["delta_kv_heads"], z["dim"], z["dim"], 4
+    C = 2 * Gd * dk + Hd * dv
+    ld = C + Hd * dv + 2 * Hd
+    tail_off = Hd * dv * dk
+    conv = torch.randn(C, taps, device=dev) * 0.5
+    a_log, dt_bias, norm_w = torch.zeros(Hd, device=dev), torch.zeros(Hd, device=dev), torch.ones(dv, device=dev)
+    for name, q_lens in (("prompt_2048", [2048]), ("prompt_8x2048", [2048] * 8), ("decode_64", [1] * 64), ("decode_256", [1] * 256)):
+        ctx, tables, n, B, _ = step_ctx(q_lens, q_lens[0])
+        state = torch.zeros(B, tail_off + (taps - 1) * C, device=dev)
+        proj = torch.randn(n, ld, device=dev)
+        mix, gates = ops.delta_prepare(proj, ld - 2 * Hd, ld - Hd, conv, a_log, dt_bias, state, tail_off, ctx, Hd, Gd, dk, dv, taps, dk ** -0.5, 1e-6)
+        ms_p = _time(lambda: ops.delta_prepare(proj, ld - 2 * Hd, ld - Hd, conv, a_log, dt_bias, state, tail_off, ctx, Hd, Gd, dk, dv, taps, dk ** -0.5, 1e-6), iters)
+        ms_r = _time(lambda: ops.delta_recurrence(mix, gates, proj, state, tail_off, ctx, Hd, Gd, dk, dv, taps), iters)
+        o32 = ops.delta_recurrence(mix, gates, proj, state, tail_off, ctx, Hd, Gd, dk, dv, taps)
+        ms_n = _time(lambda: ops.gated_rmsnorm(o32, proj[:, C:C + Hd * dv], norm_w, 1e-5, Hd, dv, torch.bfloat16), iters)
+        rec = dict(prepare_ms=round(ms_p, 4), recurrence_ms=round(ms_r, 4), out_norm_ms=round(ms_n, 4))
+        b_prep = n * (C * 4 * 2 + 2 * Hd * 4 * 2)                       # rows read, mix and gates written
+        rec["prepare_frac_of_measured"] = round(b_prep / ms_p / 1e6 / pk["hbm_gbs"], 4)
+        b_norm = n * Hd * dv * (4 + 4 + 2)
+        rec["out_norm_frac_of_measured"] = round(b_norm / ms_n / 1e6 / pk["hbm_gbs"], 4)
+        if name.startswith("decode"):
+            nbytes = B * Hd * dk * dv * 4 * 2                             # every state read and written once
+            rec["recurrence_gbs"] = round(nbytes / ms_r / 1e6, 1)
+            rec["recurrence_frac_of_measured"] = round(nbytes / ms_r / 1e6 / pk["hbm_gbs"], 4)
+        else:
+            flops = 7.0 * n * Hd * dk * dv                                # decay, S^T k, k u^T, S^T q in float32
+            rec["recurrence_fp32_tflops"] = round(flops / ms_r / 1e9, 2)
+        out[f"delta_{name}"] = rec
+    return out
+
+
+DESIGNS = {
+    "vabanex": (VABANEX_SIZES, vabanex_config_json, latent_attention_alone, "latent_attention_alone"),
+    "lupusun": (LUPUSUN_SIZES, lupusun_config_json, lupusun_kernels_alone, "kernels_alone"),
+}
+
+
 def run_design(a) -> int:
-    """Prompt and decode throughput of the Vabanex design at layer sizes of real models (random weights, bfloat16)
-    beside the Llama model of equal size, with the device time of every part of a prompt step and the latent
-    attention kernel by itself.  One JSON line."""
+    """Prompt and decode throughput of a second design at layer sizes of real models (random weights, bfloat16)
+    beside the Llama model of equal size, with the device time of every part of a prompt step and the design's own
+    kernels by themselves.  One JSON line."""
     import torch
     from batchspec_b200.config import config_from_json_dict
     from batchspec_b200.engine import Engine
@@ -402,9 +537,10 @@ def run_design(a) -> int:
     layers = a.layers or 4
     out = {"design": a.design, "layers": layers, "dtype": "bf16", "data": "synthetic", "prompt_len": PROMPT_LEN,
            "peaks": pk["source"], "sizes": {}}
-    for size, z in VABANEX_SIZES.items():
+    sizes, config_json, alone, alone_key = DESIGNS[a.design]
+    for size, z in sizes.items():
         rec = {}
-        for label, cj in (("vabanex", vabanex_config_json(z, layers)), ("llama", llama_config_json(z, layers))):
+        for label, cj in ((a.design, config_json(z, layers)), ("llama", llama_config_json(z, layers))):
             cfg = config_from_json_dict(cj)
             eng = Engine(dtype="bfloat16", device="cuda:0")
             eng.load_model(config=cfg, random_seed=0, draw_on_device=True)
@@ -420,7 +556,7 @@ def run_design(a) -> int:
             rec[label] = r
             del eng
             torch.cuda.empty_cache()
-        rec["latent_attention_alone"] = latent_attention_alone(z, pk)
+        rec[alone_key] = alone(z, pk)
         out["sizes"][size] = rec
     print(json.dumps(out))
     return 0
@@ -485,7 +621,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (no prefill, b1, b64, e2e)")
     ap.add_argument("--skip-workloads", action="store_true",
                     help="leave out e2e at batch 64 and the 3B / long-context workloads (about a minute)")
-    ap.add_argument("--design", default=None, choices=["vabanex"],
+    ap.add_argument("--design", default=None, choices=["vabanex", "lupusun"],
                     help="instead of the headline workload: this design at real layer sizes beside the Llama model of equal size")
     a = ap.parse_args()
     if a.impl == "reference":

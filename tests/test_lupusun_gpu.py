@@ -176,7 +176,7 @@ def _paged(ops, dtype, Hq, G, hd, vd, ps, q_lens, kv_lens, seed):
     return ks, vs, cache, ctx, tables, fill, qo
 
 
-def _attention_case(ops, dtype, Hq, G, hd, vd, ps, chunk, q_lens, kv_lens, sink, spike=None, seed=0):
+def _attention_case(ops, dtype, Hq, G, hd, vd, ps, chunk, q_lens, kv_lens, sink, spike=None, seed=0, plain_part=False):
     ks, vs, cache, ctx, tables, fill, qo = _paged(ops, dtype, Hq, G, hd, vd, ps, q_lens, kv_lens, seed)
     g = torch.Generator(device=DEV).manual_seed(seed + 5)
     n = sum(q_lens)
@@ -191,8 +191,14 @@ def _attention_case(ops, dtype, Hq, G, hd, vd, ps, chunk, q_lens, kv_lens, sink,
     q = q.to(dtype)
     fill()
     out = torch.full((n, Hq * vd), float("nan"), device=DEV, dtype=dtype)
-    ops.masked_attention(q.view(n, Hq * hd), out, cache, ctx, tables, Hq, G, hd, vd, 0.25, 0, chunk, sink)
+    if plain_part:          # the plain attention part's kernels (tensor cores in bfloat16), which need vd == hd
+        ctx.kv_len = _i32(kv_lens)
+        ops.paged_attention(q.view(n, Hq * hd), out, cache.view(cache.shape[0], 2, -1), ctx, tables, Hq, G, hd, 0.25, 0,
+                            chunk, sink, ops.sink_table(sink) if sink is not None else None)
+    else:
+        ops.masked_attention(q.view(n, Hq * hd), out, cache, ctx, tables, Hq, G, hd, vd, 0.25, 0, chunk, sink)
     torch.cuda.synchronize()
+    ops.check_status()
     want = torch.empty(n, Hq, vd, dtype=F64)
     for e, (ql, L) in enumerate(zip(q_lens, kv_lens)):
         pos = torch.arange(L)
@@ -239,6 +245,42 @@ def test_one_key_decides_inside_its_chunk_and_is_unseen_outside(ops, dtype, key)
                                         seed=key)
         t = sum(q_lens) - 1
         assert (got - want).abs().max() <= (1e-4 if dtype == torch.float32 else 2.5e-2)
+        hit = (got[t, 3] - vs[1][key, 1].double().cpu()).abs().max() < 0.05
+        assert hit == (key >= 1024), key
+
+
+TENSOR_CORE_SHAPES = [
+    (8, 2, 64, 64, 16, 128, [1, 1, 1, 1], [300, 17, 128, 129]),          # decode over a chunk's edge and far inside
+    (8, 2, 64, 64, 8, 100, [70, 2, 1], [200, 5, 333]),                   # chunks that are no multiples of the page
+    (4, 4, 128, 128, 16, 512, [1, 1], [1300, 513]),
+    (4, 1, 128, 128, 16, 200, [300, 130, 1], [700, 130, 801]),           # long portions: the tcgen05 kernel
+    (16, 4, 128, 128, 32, 0, [257, 3], [600, 40]),                       # a sink without a chunk mask
+    (2, 1, 256, 256, 16, 64, [40, 1, 2], [100, 640, 66]),
+    (32, 8, 128, 128, 16, 1024, [1] * 8, [4000, 1024, 1025, 2047, 2048, 2049, 31, 5000]),
+]
+
+
+@pytest.mark.parametrize("with_sink", [True, False])
+@pytest.mark.parametrize("shape", TENSOR_CORE_SHAPES, ids=lambda s: f"H{s[0]}G{s[1]}d{s[2]}ps{s[4]}c{s[5]}")
+def test_chunk_mask_and_sink_on_the_tensor_core_kernels(ops, shape, with_sink):
+    Hq = shape[0]
+    sink = torch.linspace(-2.0, 3.0, Hq, device=DEV) if with_sink else None
+    got, want, _ = _attention_case(ops, torch.bfloat16, *shape, sink=sink, seed=shape[2] + shape[5], plain_part=True)
+    assert not torch.isnan(got).any()
+    assert (got - want).abs().max() <= 2.5e-2
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("key", [0, 511, 512, 513, 527, 528, 1023, 1024, 1025, 1100, 1299])
+def test_one_key_decides_on_the_tensor_core_kernels(ops, hd, key):
+    """The same as above on the kernels that bfloat16 heads of 64 and 128 run on: split keys for the decoded token,
+    the 64-row and tcgen05 kernels for the portion."""
+    for q_lens in ([1, 1], [3, 300]):
+        sink = torch.tensor([0.5, -0.5, 0.0, 1.0], device=DEV)
+        got, want, vs = _attention_case(ops, torch.bfloat16, 4, 2, hd, hd, 16, 512, q_lens, [90, 1300], sink,
+                                        spike=(1, key, 3), seed=key, plain_part=True)
+        t = sum(q_lens) - 1
+        assert (got - want).abs().max() <= 2.5e-2
         hit = (got[t, 3] - vs[1][key, 1].double().cpu()).abs().max() < 0.05
         assert hit == (key >= 1024), key
 
