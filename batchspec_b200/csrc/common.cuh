@@ -129,6 +129,15 @@ __device__ __forceinline__ void pdl_prologue(int kid = 0) {
   trace_record(kid, t0);
 }
 
+// For a long kernel whose successor would only sit on the SMs: wait for the predecessor, and let the kernel call
+// pdl_launch_dependents() itself when its main loop is over.  (Measured on B200: a recurrence kernel of a millisecond
+// ran twice as long while the blocks of the next kernel, launched at its start, waited beside it.)
+__device__ __forceinline__ void pdl_prologue_late(int kid = 0) {
+  const unsigned long long t0 = g_trace_buf != nullptr ? global_timer() : 0ull;
+  pdl_wait();
+  trace_record(kid, t0);
+}
+
 // Facts about a device are kept per device: a process may use several.
 constexpr int kMaxDevices = 64;
 inline int current_device() {
@@ -154,6 +163,25 @@ inline bool& pdl_enabled() {
 }
 
 // Launch with the programmatic-stream-serialization attribute (when enabled) and, optionally, a cluster along z.
+// ``serialized``: without the attribute, i.e. the kernel starts when its predecessor has ended.  For a kernel of few,
+// long-lived blocks: launched early, its blocks go wherever the predecessor's blocks happen to end first, several to
+// one SM and none to others (measured on B200: a recurrence kernel of 256 blocks ran 1.9x as long that way).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args... args);
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_serialized(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.attrs = nullptr;
+  cfg.numAttrs = 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                           Args... args) {
@@ -174,6 +202,8 @@ inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
 
 #define BSPEC_LAUNCH(kernel, grid, block, smem, stream, ...) \
   (void)bspec::launch(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__)
+#define BSPEC_LAUNCH_SERIALIZED(kernel, grid, block, smem, stream, ...) \
+  (void)bspec::launch_serialized(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__)
 #define BSPEC_LAUNCH_CHECK() (int)cudaGetLastError()
 // Reads (and clears) the translation unit's record of the checked build into out4; returns 1 in a checked build,
 // 0 otherwise (out4 zeroed), a negative CUDA error on failure.  Waits for the device.

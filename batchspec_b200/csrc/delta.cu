@@ -7,7 +7,7 @@
 //   delta_prepare     per token: causal short convolution + silu of the q, k, v channels (the inputs before the
 //                     portion come from the request's state), unit length of every q and k head (q also times a
 //                     scale), beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias))
-//   delta_recurrence  per (request, head, 32 value columns): the token loop over the portion with the state in
+//   delta_recurrence  per (request, head, 32 or 8 value columns): the token loop over the portion with the state in
 //                     registers (a column of S is spread over four lanes), state read at the start and written at
 //                     the end; one block per request also moves the convolutions' inputs on
 //   gated_rmsnorm     per (token, head): o / rms(o) * w * silu(gate)
@@ -15,6 +15,7 @@
 // The order of every sum depends on the sizes alone, not on how a request was cut into portions or on what else is
 // in the step.
 #include "common.cuh"
+#include <cuda_pipeline.h>
 #include <math.h>
 using namespace bspec;
 
@@ -69,25 +70,31 @@ delta_prepare_kernel(const float* __restrict__ proj, int ld, int b_off, int a_of
   }
 }
 
-constexpr int COLS = 32;          // value columns of a block
-constexpr int LANES = 4;          // lanes that share one column of S
-constexpr int TILE = 8;           // tokens whose q, k, v, beta, g are staged in shared memory at a time
 constexpr int MAX_DIM = 256;
 
-// R: floats of a column that one lane holds (a multiple of 4, dim <= 4 R).  A lane holds rows 16 c + 4 r + {0..3}
-// for c < R / 4, so that the four lanes of a column read 64 contiguous bytes of state at a time.
-template <int R>
+// LANES: lanes that share one column of S; R: floats of the column that one lane holds (a multiple of 4, dim <=
+// LANES R); COLS: value columns of a block.  Lane r holds rows 4 LANES c + 4 r + {0..3} for c < R / 4, so that the
+// lanes of a column read contiguous bytes of state at a time.  Many short columns per block (LANES 4, COLS 32) when
+// the step has enough (request, head) pairs to fill the device; else (one long prompt) a column is spread over 16
+// lanes and a block holds 8 columns, which makes four times as many warps with dependent chains a quarter as long.  Per token both read-outs are taken from the state before the write,
+//     a = S^T k,  b = S^T q,  u = beta (v - g a),  o = g b + u (k . q),  S <- g S + k u^T,
+// which is the rule above with o = (g S + k u^T)^T q multiplied out: one pass over the registers for the three sums
+// (reduced over the column's lanes together), one for the update.  The next tile of tokens is copied into the
+// other half of the staging buffers while the current one is worked on.
+template <int R, int COLS, int LANES>
 __global__ void __launch_bounds__(COLS * LANES)
 delta_recurrence_kernel(const float* __restrict__ mix, const float* __restrict__ gates, const float* __restrict__ proj,
                         int ld, float* __restrict__ state, long long state_stride, long long tail_off,
                         const int* __restrict__ qo_indptr, const int* __restrict__ state_slots,
                         float* __restrict__ out, int H, int Gk, int dim, int vdim, int taps) {
-  bspec::pdl_prologue(61);
+  bspec::pdl_prologue_late(61);
+  constexpr int NT = COLS * LANES, DP = LANES * R;
+  constexpr int TILE = DP > 128 ? 8 : 16;          // tokens whose q, k, v, beta, g are staged in shared memory at a time
   const int dimp = (dim + 3) & ~3;                 // a column of S is kept padded to whole float4s; the pad stays 0
-  __shared__ __align__(16) float qs[TILE][MAX_DIM];
-  __shared__ __align__(16) float ks[TILE][MAX_DIM];
-  __shared__ float vs[TILE][COLS];
-  __shared__ float bg[TILE][2];
+  __shared__ __align__(16) float qs[2][TILE][DP];
+  __shared__ __align__(16) float ks[2][TILE][DP];
+  __shared__ float vs[2][TILE][COLS];
+  __shared__ float bg[2][TILE][2];
   const int e = blockIdx.z, h = blockIdx.y;
   const int q_begin = qo_indptr[e], n = qo_indptr[e + 1] - q_begin;
   const int C = 2 * Gk * dim + H * vdim;
@@ -97,7 +104,7 @@ delta_recurrence_kernel(const float* __restrict__ mix, const float* __restrict__
     // the convolutions' inputs: slot s holds the input at index n + s - (taps - 1) of this portion, or what an
     // older slot held; ascending s, so that a slot is read before it is overwritten
     float* tail = srow + tail_off;
-    for (int c = threadIdx.x; c < C; c += blockDim.x)
+    for (int c = threadIdx.x; c < C; c += NT)
       for (int s = 0; s < taps - 1; ++s) {
         const int rel = n + s - (taps - 1);
         tail[(size_t)s * C + c] = rel >= 0 ? proj[(size_t)(q_begin + rel) * ld + c] : tail[(size_t)(s + n) * C + c];
@@ -107,69 +114,112 @@ delta_recurrence_kernel(const float* __restrict__ mix, const float* __restrict__
   const int j = blockIdx.x * COLS + col;
   const bool live = j < vdim;
   const int kh = h / (H / Gk);
+  // the pad of a row is never copied into: zero it once in both halves
+  for (int w = threadIdx.x; w < 2 * TILE * (DP - dim); w += NT) {
+    const int bt = w / (DP - dim), d = dim + w % (DP - dim);
+    qs[bt / TILE][bt % TILE][d] = 0.f;
+    ks[bt / TILE][bt % TILE][d] = 0.f;
+  }
+  auto stage = [&](int t0, int buf) {              // asynchronous copies of tokens t0 .. t0 + TILE - 1 of the portion
+    const int nt = min(TILE, n - t0);
+    if (((dim | C) & 3) == 0) {                    // rows of q and k start on 16-byte boundaries
+      for (int tt = threadIdx.x >> 5; tt < nt; tt += NT / 32) {        // a warp per token: equal work for all warps
+        const float* row = mix + (size_t)(q_begin + t0 + tt) * C;
+        for (int d = 4 * (threadIdx.x & 31); d < dim; d += 128) {
+          __pipeline_memcpy_async(&qs[buf][tt][d], row + kh * dim + d, 16);
+          __pipeline_memcpy_async(&ks[buf][tt][d], row + (Gk + kh) * dim + d, 16);
+        }
+      }
+    } else {
+      for (int w = threadIdx.x; w < nt * dim; w += NT) {
+        const int tt = w / dim, d = w - tt * dim;
+        const float* row = mix + (size_t)(q_begin + t0 + tt) * C;
+        __pipeline_memcpy_async(&qs[buf][tt][d], row + kh * dim + d, 4);
+        __pipeline_memcpy_async(&ks[buf][tt][d], row + (Gk + kh) * dim + d, 4);
+      }
+    }
+    for (int w = threadIdx.x; w < nt * COLS; w += NT) {
+      const int tt = w / COLS, cc = w - tt * COLS;
+      const int jj = blockIdx.x * COLS + cc;
+      if (jj < vdim)
+        __pipeline_memcpy_async(&vs[buf][tt][cc], mix + (size_t)(q_begin + t0 + tt) * C + 2 * Gk * dim + h * vdim + jj, 4);
+    }
+    if (threadIdx.x < nt * 2) {
+      const int tt = threadIdx.x >> 1, which = threadIdx.x & 1;
+      __pipeline_memcpy_async(&bg[buf][tt][which], gates + (size_t)(q_begin + t0 + tt) * 2 * H + which * H + h, 4);
+    }
+    __pipeline_commit();
+  };
+  stage(0, 0);
   float s[R];
   float* sp = srow + ((size_t)h * vdim + (live ? j : 0)) * dimp;
 #pragma unroll
   for (int c = 0; c < R / 4; ++c) {
-    const int row = 16 * c + 4 * r;
+    const int row = 4 * LANES * c + 4 * r;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (live && row < dimp) v = *reinterpret_cast<const float4*>(sp + row);
     s[4 * c] = v.x; s[4 * c + 1] = v.y; s[4 * c + 2] = v.z; s[4 * c + 3] = v.w;
   }
-  for (int t0 = 0; t0 < n; t0 += TILE) {
+  int buf = 0;
+  for (int t0 = 0; t0 < n; t0 += TILE, buf ^= 1) {
     const int nt = min(TILE, n - t0);
-    __syncthreads();
-    for (int w = threadIdx.x; w < nt * dimp; w += blockDim.x) {
-      const int tt = w / dimp, d = w - tt * dimp;
-      const float* row = mix + (size_t)(q_begin + t0 + tt) * C;
-      qs[tt][d] = d < dim ? row[kh * dim + d] : 0.f;
-      ks[tt][d] = d < dim ? row[(Gk + kh) * dim + d] : 0.f;
-    }
-    for (int w = threadIdx.x; w < nt * COLS; w += blockDim.x) {
-      const int tt = w / COLS, cc = w - tt * COLS;
-      const int jj = blockIdx.x * COLS + cc;
-      vs[tt][cc] = jj < vdim ? mix[(size_t)(q_begin + t0 + tt) * C + 2 * Gk * dim + h * vdim + jj] : 0.f;
-    }
-    if (threadIdx.x < nt * 2) {
-      const int tt = threadIdx.x >> 1, which = threadIdx.x & 1;
-      bg[tt][which] = gates[(size_t)(q_begin + t0 + tt) * 2 * H + which * H + h];
-    }
-    __syncthreads();
+    __pipeline_wait_prior(0);
+    __syncthreads();                                // the tile is there, and every thread is done with the other half
+    if (t0 + TILE < n) stage(t0 + TILE, buf ^ 1);
+    // the token's k and q live in registers for both passes; with few floats per lane the next token's are
+    // fetched before this token's sums are reduced
+    constexpr bool AHEAD = R <= 16;
+    float4 kr[R / 4], qr[R / 4], kn[AHEAD ? R / 4 : 1], qn[AHEAD ? R / 4 : 1];
+    auto fetch = [&](int tt, float4* kd, float4* qd) {
+#pragma unroll
+      for (int c = 0; c < R / 4; ++c) {
+        const int row = 4 * LANES * c + 4 * r;      // rows beyond dim hold zeros in the state and in the staging
+        kd[c] = *reinterpret_cast<const float4*>(&ks[buf][tt][row]);
+        qd[c] = *reinterpret_cast<const float4*>(&qs[buf][tt][row]);
+      }
+    };
+    if (AHEAD) fetch(0, kn, qn);
     for (int tt = 0; tt < nt; ++tt) {
-      const float beta = bg[tt][0], g = bg[tt][1];
-      float dk = 0.f;
+      const float beta = bg[buf][tt][0], g = bg[buf][tt][1], vj = vs[buf][tt][col];
+      if (AHEAD) {
+#pragma unroll
+        for (int c = 0; c < R / 4; ++c) { kr[c] = kn[c]; qr[c] = qn[c]; }
+      } else {
+        fetch(tt, kr, qr);
+      }
+      float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f, kq = 0.f;
 #pragma unroll
       for (int c = 0; c < R / 4; ++c) {
-        const int row = 16 * c + 4 * r;
-        if (row < dimp) {
-          const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][row]);
-          s[4 * c] *= g; s[4 * c + 1] *= g; s[4 * c + 2] *= g; s[4 * c + 3] *= g;
-          dk += s[4 * c] * k4.x; dk += s[4 * c + 1] * k4.y; dk += s[4 * c + 2] * k4.z; dk += s[4 * c + 3] * k4.w;
-        }
+        const float4 k4 = kr[c], q4 = qr[c];
+        a0 += s[4 * c] * k4.x; a1 += s[4 * c + 1] * k4.y; a0 += s[4 * c + 2] * k4.z; a1 += s[4 * c + 3] * k4.w;
+        b0 += s[4 * c] * q4.x; b1 += s[4 * c + 1] * q4.y; b0 += s[4 * c + 2] * q4.z; b1 += s[4 * c + 3] * q4.w;
+        kq += k4.x * q4.x; kq += k4.y * q4.y; kq += k4.z * q4.z; kq += k4.w * q4.w;
       }
-      dk += __shfl_xor_sync(0xffffffffu, dk, 1);
-      dk += __shfl_xor_sync(0xffffffffu, dk, 2);
-      const float u = beta * (vs[tt][col] - dk);
-      float dq = 0.f;
+      if (AHEAD && tt + 1 < nt) fetch(tt + 1, kn, qn);
+      float a = a0 + a1, b = b0 + b1;
+#pragma unroll
+      for (int o = 1; o < LANES; o <<= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, o);
+        b += __shfl_xor_sync(0xffffffffu, b, o);
+        kq += __shfl_xor_sync(0xffffffffu, kq, o);
+      }
+      const float u = beta * (vj - g * a);
+      if (live && r == 0) out[(size_t)(q_begin + t0 + tt) * H * vdim + h * vdim + j] = g * b + u * kq;
 #pragma unroll
       for (int c = 0; c < R / 4; ++c) {
-        const int row = 16 * c + 4 * r;
-        if (row < dimp) {
-          const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][row]);
-          const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][row]);
-          s[4 * c] += k4.x * u; s[4 * c + 1] += k4.y * u; s[4 * c + 2] += k4.z * u; s[4 * c + 3] += k4.w * u;
-          dq += s[4 * c] * q4.x; dq += s[4 * c + 1] * q4.y; dq += s[4 * c + 2] * q4.z; dq += s[4 * c + 3] * q4.w;
-        }
+        const float4 k4 = kr[c];
+        s[4 * c] = fmaf(k4.x, u, g * s[4 * c]);
+        s[4 * c + 1] = fmaf(k4.y, u, g * s[4 * c + 1]);
+        s[4 * c + 2] = fmaf(k4.z, u, g * s[4 * c + 2]);
+        s[4 * c + 3] = fmaf(k4.w, u, g * s[4 * c + 3]);
       }
-      dq += __shfl_xor_sync(0xffffffffu, dq, 1);
-      dq += __shfl_xor_sync(0xffffffffu, dq, 2);
-      if (live && r == 0) out[(size_t)(q_begin + t0 + tt) * H * vdim + h * vdim + j] = dq;
     }
   }
+  bspec::pdl_launch_dependents();
   if (live) {
 #pragma unroll
     for (int c = 0; c < R / 4; ++c) {
-      const int row = 16 * c + 4 * r;
+      const int row = 4 * LANES * c + 4 * r;
       if (row < dimp) *reinterpret_cast<float4*>(sp + row) = make_float4(s[4 * c], s[4 * c + 1], s[4 * c + 2], s[4 * c + 3]);
     }
   }
@@ -223,10 +273,20 @@ BSPEC_API int bspec_delta_recurrence(const float* mix, const float* gates, const
   if (n_entries <= 0) return 0;
   if (dim <= 0 || dim > MAX_DIM || H % Gk != 0 || n_entries > 65535 || H > 65535)
     return (int)cudaErrorInvalidValue;
-  const dim3 grid((vdim + COLS - 1) / COLS, H, n_entries);
-#define LR(R) BSPEC_LAUNCH((delta_recurrence_kernel<R>), grid, COLS * LANES, 0, stream, mix, gates, proj, ld, state, \
-                           state_stride, tail_off, qo_indptr, state_slots, out, H, Gk, dim, vdim, taps)
-  if (dim <= 32) LR(8); else if (dim <= 64) LR(16); else if (dim <= 128) LR(32); else LR(64);
+  // 32 value columns of 4 lanes per block; 8 columns of 16 lanes when that would leave most of the device idle
+  const bool narrow = (long long)((vdim + 31) / 32) * H * n_entries < 2ll * bspec::sm_count();
+  const int cols = narrow ? 8 : 32;
+  const dim3 grid((vdim + cols - 1) / cols, H, n_entries);
+#define LR(R4, R16)                                                                                                \
+  do {                                                                                                             \
+    if (narrow)                                                                                                    \
+      BSPEC_LAUNCH_SERIALIZED((delta_recurrence_kernel<R16, 8, 16>), grid, 8 * 16, 0, stream, mix, gates, proj, ld, state, \
+                   state_stride, tail_off, qo_indptr, state_slots, out, H, Gk, dim, vdim, taps);                   \
+    else                                                                                                           \
+      BSPEC_LAUNCH_SERIALIZED((delta_recurrence_kernel<R4, 32, 4>), grid, 32 * 4, 0, stream, mix, gates, proj, ld, state,     \
+                   state_stride, tail_off, qo_indptr, state_slots, out, H, Gk, dim, vdim, taps);                   \
+  } while (0)
+  if (dim <= 32) LR(8, 4); else if (dim <= 64) LR(16, 4); else if (dim <= 128) LR(32, 8); else LR(64, 16);
 #undef LR
   return BSPEC_LAUNCH_CHECK();
 }
