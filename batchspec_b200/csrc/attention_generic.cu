@@ -11,7 +11,7 @@
 //
 // Masks: causal; ``window`` > 0 keeps the last ``window`` keys; ``chunk`` > 0 keeps the keys of the query's own
 // chunk, floor(key / chunk) == floor(query / chunk), chunks counted from position 0 of the request.  ``sink``: one
-// float32 per query head that joins the softmax denominator as exp(sink) and has no value.
+// float32 per query head: exp(sink) is added to the softmax denominator, nothing to the numerator.
 #include "common.cuh"
 #include <math.h>
 using namespace bspec;
@@ -92,7 +92,7 @@ attn_generic_kernel(const T* __restrict__ q, long long q_row_stride, T* __restri
     }
     m = m_new;
   }
-  if (sink != nullptr) {                                // one more term of the denominator, without a value
+  if (sink != nullptr) {                                // one more term of the denominator only
     const float sk = sink[h];
     const float m_new = fmaxf(m, sk);
     const float corr = expf(m - m_new);
@@ -160,7 +160,7 @@ BSPEC_API int bspec_attention_masked(const void* q, long long q_row_stride, void
 // all in float32; then write q to ``q_out`` [n, Hq*hd] and k and v into the cache page of the token's position.
 // One warp per head.
 namespace {
-constexpr int PREP_WARPS = 4;
+constexpr int PREP_WARPS = 8;
 
 __device__ __forceinline__ void prep_sincos(int pos, const float* __restrict__ inv_freq, int half, int j, float* s,
                                             float* c) {
@@ -179,11 +179,22 @@ qkv_prepare_kernel(const float* __restrict__ qkv, int Hq, int Hkv, int hd, int v
                    T* __restrict__ cache, int page_size, int write_kv, long long n_pages) {
   bspec::pdl_prologue(19);
   __shared__ float xs[PREP_WARPS][MAX_HD];
+  __shared__ float cs[MAX_HD];                                // [rot/2] cosines, then [rot/2] sines, of this token
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slot = blockIdx.y * PREP_WARPS + warp;            // q heads, then k heads, then v heads
-  if (slot >= Hq + 2 * Hkv) return;
   const int pos = positions[t];
+  if (blockIdx.y * PREP_WARPS < Hq + Hkv) {                   // the block holds a q or k head: the angles once for all
+    const int half = rot / 2;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+      float sn, c;
+      prep_sincos(pos, inv_freq, half, j, &sn, &c);
+      cs[j] = c * magnitude;
+      cs[half + j] = sn * magnitude;
+    }
+  }
+  __syncthreads();
+  if (slot >= Hq + 2 * Hkv) return;
   const int ld = (Hq + Hkv) * hd + Hkv * vd;
   const bool is_v = slot >= Hq + Hkv;
   const int width = is_v ? vd : hd;
@@ -197,10 +208,7 @@ qkv_prepare_kernel(const float* __restrict__ qkv, int Hq, int Hkv, int hd, int v
   if (!is_v) {
     const int half = rot / 2;
     for (int j = lane; j < half; j += 32) {
-      float sn, c;
-      prep_sincos(pos, inv_freq, half, j, &sn, &c);
-      sn *= magnitude;
-      c *= magnitude;
+      const float c = cs[j], sn = cs[half + j];
       const int a = interleaved ? 2 * j : j, b = interleaved ? 2 * j + 1 : j + half;
       const float u = x[a], v = x[b];
       x[a] = u * c - v * sn;

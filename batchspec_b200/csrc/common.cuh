@@ -43,7 +43,7 @@ __device__ __forceinline__ float warp_max(float v) {
 __device__ __forceinline__ int mask_lo(int pos, int window) {
   return window > 0 ? max(0, pos - window + 1) : (window < 0 ? (pos / -window) * -window : 0);
 }
-// A softmax sink joins the denominator as exp(sink) and has no value.  With the running maximum ``m`` and sum ``l``
+// A softmax sink is a logit per head that adds exp(sink) to the denominator and nothing to the numerator.  With the running maximum ``m`` and sum ``l``
 // in base-2 units and ``sink_l2`` = sink * log2(e) per query head (null: none): the sum with the sink's term.
 __device__ __forceinline__ float with_sink(float l, float m, const float* __restrict__ sink_l2, int h) {
   return sink_l2 != nullptr && l > 0.f ? l + exp2f(sink_l2[h] - m) : l;

@@ -6,8 +6,8 @@
 * ``qk_norm_eps``: after the rotation every q and k head is divided by its root mean square (no weight);
 * a mask besides causality: ``chunk`` (a query sees the keys of its own chunk of ``chunk`` positions, counted from
   position 0 of the request) or ``window`` (the last ``window`` keys);
-* ``sink``: a learned number per query head that enters the softmax denominator as exp(sink), with no key and no
-  value: out_h(i) = sum_j exp(s_ij) v_j / (exp(sink_h) + sum_j exp(s_ij)).
+* ``sink``: a learned logit per query head that takes part in the normalisation only:
+  out_h(i) = sum_j exp(s_ij) v_j / (exp(sink_h) + sum_j exp(s_ij)).
 
 Launch sequence: one product for [Wq; Wk; Wv] with float32 output -> q/k/v preparation (bias, rotation, norms, all
 float32; q in the run dtype, k and v into their cache pages) -> attention over the pages -> output projection.

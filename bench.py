@@ -459,7 +459,7 @@ def lupusun_kernels_alone(z, pk, iters=20):
         cache = torch.randn(B * pages_per, 2, ps * G * hd, device=dev).bfloat16()
         q = torch.randn(n, Hq * hd, device=dev).bfloat16()
         o = torch.empty(n, Hq * hd, device=dev, dtype=torch.bfloat16)
-        for label, ck, sk, sk2 in (("chunk_sink", chunk, sink, sink_l2), ("causal", 0, None, None)):
+        for label, ck, sk, sk2 in (("chunk_sink", chunk, sink, sink_l2), ("sink", 0, sink, sink_l2), ("causal", 0, None, None)):
             ctx.extras = {"min_q_len": min(q_lens)}
             ms = _time(lambda: ops.paged_attention(q, o, cache, ctx, tables, Hq, G, hd, hd ** -0.5, 0, ck, sk, sk2), iters)
             span = ck or (1 << 30)

@@ -123,7 +123,7 @@ def test_plain_attention_mask_sink_and_groups():
             s = torch.stack([(q[i, h] @ k[j, h // 2]) * 0.4 for j in js])
             w = torch.exp(s) / (torch.exp(s).sum() + torch.exp(sink[h]))
             assert torch.allclose(out[i, h], sum(w[n] * v[j, h // 2] for n, j in enumerate(js)), atol=1e-12)
-    assert out[:, 3].abs().max() < 1e-9                 # a huge sink takes all the weight and has no value
+    assert out[:, 3].abs().max() < 1e-9                 # a huge sink takes all the weight and gives nothing back
     # shifting all positions by a multiple of the chunk changes nothing; by another amount it does
     assert torch.allclose(P.chunked_sink_attention(q, k, v, sink, 0.4, size, pos + 3 * size), out)
     assert not torch.allclose(P.chunked_sink_attention(q, k, v, sink, 0.4, size, pos + 2), out)
