@@ -170,6 +170,17 @@ __device__ __forceinline__ void prep_sincos(int pos, const float* __restrict__ i
   sincosf((float)a, s, c);
 }
 
+__device__ __forceinline__ void prep_store4(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void prep_store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 v;
+  v.x = *reinterpret_cast<const uint32_t*>(&lo);
+  v.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = v;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(PREP_WARPS * 32)
 qkv_prepare_kernel(const float* __restrict__ qkv, int Hq, int Hkv, int hd, int vd, const void* __restrict__ bias,
@@ -178,12 +189,26 @@ qkv_prepare_kernel(const float* __restrict__ qkv, int Hq, int Hkv, int hd, int v
                    const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, T* __restrict__ q_out,
                    T* __restrict__ cache, int page_size, int write_kv, long long n_pages) {
   bspec::pdl_prologue(19);
-  __shared__ float xs[PREP_WARPS][MAX_HD];
+  __shared__ __align__(16) float xs[PREP_WARPS][MAX_HD];
   __shared__ float cs[MAX_HD];                                // [rot/2] cosines, then [rot/2] sines, of this token
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slot = blockIdx.y * PREP_WARPS + warp;            // q heads, then k heads, then v heads
   const int pos = positions[t];
+  const int ld = (Hq + Hkv) * hd + Hkv * vd;
+  const bool has = slot < Hq + 2 * Hkv;
+  const bool is_v = slot >= Hq + Hkv;
+  const int width = is_v ? vd : hd;
+  const int col0 = is_v ? (Hq + Hkv) * hd + (slot - Hq - Hkv) * vd : slot * hd;
+  const float* src = qkv + (size_t)t * ld + (has ? col0 : 0);
+  float* x = xs[warp];
+  const bool vec = ((hd | vd) & 3) == 0;           // every head starts on a 16-byte boundary: four numbers per lane
+  // the head's numbers are asked for first, so that their way from memory runs under the angles' arithmetic
+  float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+  if (has && vec) {
+    if (4 * lane < width) v0 = *reinterpret_cast<const float4*>(src + 4 * lane);
+    if (4 * lane + 128 < width) v1 = *reinterpret_cast<const float4*>(src + 4 * lane + 128);
+  }
   if (blockIdx.y * PREP_WARPS < Hq + Hkv) {                   // the block holds a q or k head: the angles once for all
     const int half = rot / 2;
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
@@ -194,15 +219,26 @@ qkv_prepare_kernel(const float* __restrict__ qkv, int Hq, int Hkv, int hd, int v
     }
   }
   __syncthreads();
-  if (slot >= Hq + 2 * Hkv) return;
-  const int ld = (Hq + Hkv) * hd + Hkv * vd;
-  const bool is_v = slot >= Hq + Hkv;
-  const int width = is_v ? vd : hd;
-  const int col0 = is_v ? (Hq + Hkv) * hd + (slot - Hq - Hkv) * vd : slot * hd;
-  const float* src = qkv + (size_t)t * ld + col0;
-  float* x = xs[warp];
-  for (int d = lane; d < width; d += 32)
-    x[d] = src[d] + (bias != nullptr ? load_as_f32(bias, bias_dtype, (size_t)col0 + d) : 0.f);
+  if (!has) return;
+  if (vec) {
+#pragma unroll
+    for (int part = 0; part < 2; ++part) {
+      const int d = 4 * lane + 128 * part;
+      if (d < width) {
+        float4 v = part ? v1 : v0;
+        if (bias != nullptr) {
+          v.x += load_as_f32(bias, bias_dtype, (size_t)col0 + d);
+          v.y += load_as_f32(bias, bias_dtype, (size_t)col0 + d + 1);
+          v.z += load_as_f32(bias, bias_dtype, (size_t)col0 + d + 2);
+          v.w += load_as_f32(bias, bias_dtype, (size_t)col0 + d + 3);
+        }
+        *reinterpret_cast<float4*>(x + d) = v;
+      }
+    }
+  } else {
+    for (int d = lane; d < width; d += 32)
+      x[d] = src[d] + (bias != nullptr ? load_as_f32(bias, bias_dtype, (size_t)col0 + d) : 0.f);
+  }
   __syncwarp();
   float ss = 0.f;
   if (!is_v) {
@@ -238,8 +274,16 @@ qkv_prepare_kernel(const float* __restrict__ qkv, int Hq, int Hkv, int hd, int v
       }
     }
   }
-  if (dst != nullptr)
-    for (int d = lane; d < width; d += 32) dst[d] = from_f32<T>(x[d] * r);
+  if (dst != nullptr) {
+    if (vec) {
+      for (int d = 4 * lane; d < width; d += 128) {
+        const float4 v = *reinterpret_cast<const float4*>(x + d);
+        prep_store4(dst + d, v.x * r, v.y * r, v.z * r, v.w * r);
+      }
+    } else {
+      for (int d = lane; d < width; d += 32) dst[d] = from_f32<T>(x[d] * r);
+    }
+  }
 }
 }  // namespace
 

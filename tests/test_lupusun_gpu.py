@@ -218,6 +218,7 @@ ATTENTION_SHAPES = [
     (8, 2, 64, 64, 16, 128, [1, 1, 1, 1], [300, 17, 128, 129]),
     (2, 2, 128, 40, 16, 50, [70, 2, 1], [200, 5, 333]),
     (5, 5, 20, 256, 8, 0, [9, 1], [40, 200]),                      # no chunk mask
+    (2, 1, 24, 16, 4, 1, [6, 1], [6, 30]),                         # chunks of one position
 ]
 
 
@@ -257,6 +258,9 @@ TENSOR_CORE_SHAPES = [
     (16, 4, 128, 128, 32, 0, [257, 3], [600, 40]),                       # a sink without a chunk mask
     (2, 1, 256, 256, 16, 64, [40, 1, 2], [100, 640, 66]),
     (32, 8, 128, 128, 16, 1024, [1] * 8, [4000, 1024, 1025, 2047, 2048, 2049, 31, 5000]),
+    (4, 2, 64, 64, 16, 24, [50, 1, 3], [120, 77, 40]),                   # chunks shorter than a tile of keys
+    (4, 4, 128, 128, 16, 1, [130, 1], [130, 300]),                       # chunks of one position: a token sees itself
+    (2, 1, 128, 128, 8, 3, [200, 2], [333, 9]),
 ]
 
 
