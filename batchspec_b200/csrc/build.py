@@ -4,8 +4,15 @@ Plain ``nvcc`` on the ``.cu`` files beside this module (no torch headers: the
 entry points are ``extern "C"`` and are called through ``ctypes`` with raw device
 pointers), objects and library under ``_build/`` beside the sources, or under a
 per-user temporary folder when the package folder cannot be written.  The library
-is rebuilt when the hash of the sources and flags changes.  Progress goes to
+is rebuilt when the hash of the sources and flags changes; an object is compiled
+again only when its own source, a header or the flags changed.  Progress goes to
 stderr, a line per file and a line every few seconds while waiting.
+
+Files that only some architectures need form *features* (``FEATURES``); everything
+else is the core.  ``library_path(features=None)`` is the library of all files;
+``library_path(features=("latent",))`` one of the core and the named features only
+(``libbspec_kernels_core+latent.so``), so that the first run of a model in a fresh
+checkout compiles what that model needs.
 """
 from __future__ import annotations
 
@@ -21,6 +28,8 @@ from typing import List, Optional
 
 CSRC = Path(__file__).resolve().parent
 LIB_NAME = "libbspec_kernels.so"
+# files that only some mixers or feed-forwards need; every other .cu file is the core
+FEATURES = {"latent": ("latent.cu", "latent_mma.cu"), "moe": ("moe.cu",)}
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
               "--expt-relaxed-constexpr"]
@@ -49,16 +58,45 @@ def find_nvcc() -> str:
     raise RuntimeError("nvcc was not found (PATH, CUDA_HOME, /usr/local/cuda): the CUDA kernels cannot be built")
 
 
-def sources() -> List[Path]:
-    return sorted(CSRC.glob("*.cu"))
+def sources(features=None) -> List[Path]:
+    """The files of the library with these features (None: all files)."""
+    every = sorted(CSRC.glob("*.cu"))
+    if features is None:
+        return every
+    unknown = set(features) - set(FEATURES)
+    if unknown:
+        raise KeyError(f"kernel features {sorted(unknown)} are not known (known: {sorted(FEATURES)})")
+    left_out = {name for f, names in FEATURES.items() if f not in features for name in names}
+    return [p for p in every if p.name not in left_out]
 
 
-def _source_hash() -> str:
+def lib_name(features=None) -> str:
+    if features is None or set(features) == set(FEATURES):
+        return LIB_NAME
+    return LIB_NAME[:-3] + "_" + "+".join(["core"] + sorted(features)) + ".so"
+
+
+def _headers_hash() -> "hashlib._Hash":
     h = hashlib.sha256()
-    for p in sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
+    for p in sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
         h.update(p.name.encode())
         h.update(p.read_bytes())
     h.update(" ".join(ARCH_FLAGS + _flags()).encode())
+    return h
+
+
+def _object_hash(src: Path) -> str:
+    h = _headers_hash()
+    h.update(src.name.encode())
+    h.update(src.read_bytes())
+    return h.hexdigest()
+
+
+def _source_hash(features=None) -> str:
+    h = _headers_hash()
+    for p in sources(features):
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
     return h.hexdigest()
 
 
@@ -81,32 +119,47 @@ def _build_dir() -> Path:
         return d
 
 
-def library_path(build: bool = True) -> Path:
-    """Path of an up-to-date library, building it first if need be."""
-    bdir = _build_dir()
-    lib, stamp = bdir / LIB_NAME, bdir / (LIB_NAME + ".hash")
-    want = _source_hash()
-    if lib.is_file() and stamp.is_file() and stamp.read_text().strip() == want:
+def _up_to_date(bdir: Path, features) -> Optional[Path]:
+    lib = bdir / lib_name(features)
+    stamp = bdir / (lib.name + ".hash")
+    if lib.is_file() and stamp.is_file() and stamp.read_text().strip() == _source_hash(features):
         return lib
+    return None
+
+
+def library_path(build: bool = True, features=None) -> Path:
+    """Path of an up-to-date library with these features (None: all files), building it first if need be.  An
+    up-to-date library of all files serves any features."""
+    bdir = _build_dir()
+    found = _up_to_date(bdir, features) or (_up_to_date(bdir, None) if features is not None else None)
+    if found is not None:
+        return found
+    lib = bdir / lib_name(features)
     if not build:
         raise FileNotFoundError(f"{lib} is missing or stale")
-    _compile(bdir, lib)
-    stamp.write_text(want + "\n")
+    _compile(bdir, lib, features)
+    (bdir / (lib.name + ".hash")).write_text(_source_hash(features) + "\n")
     return lib
 
 
-def _compile(bdir: Path, lib: Path) -> None:
+def _compile(bdir: Path, lib: Path, features=None) -> None:
     nvcc = find_nvcc()
-    srcs = sources()
-    _log(f"compiling {len(srcs)} CUDA files for sm_100a with {nvcc} into {bdir}")
+    srcs = sources(features)
     t0 = time.time()
     env = dict(os.environ)
     env.setdefault("TMPDIR", str(bdir))
-    procs = []
+    procs, objects, stamps = [], [], {}
     for src in srcs:
         obj = bdir / (src.stem + ".o")
+        objects.append(obj)
+        stamp, want = bdir / (src.stem + ".o.hash"), _object_hash(src)
+        if obj.is_file() and stamp.is_file() and stamp.read_text().strip() == want:
+            continue                                  # compiled from these very bytes before
+        stamp.unlink(missing_ok=True)
+        stamps[src] = (stamp, want)
         cmd = [nvcc, *ARCH_FLAGS, *_flags(), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
         procs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, env=env)))
+    _log(f"compiling {len(procs)} of {len(srcs)} CUDA files for sm_100a with {nvcc} into {bdir}")
     pending = list(procs)
     last = time.time()
     while pending:
@@ -120,6 +173,7 @@ def _compile(bdir: Path, lib: Path) -> None:
                             q.kill()
                     raise RuntimeError(f"nvcc failed on {src.name}:\n{out}")
                 _log(f"compiled {src.name} ({time.time() - t0:.0f}s)")
+                stamps[src][0].write_text(stamps[src][1] + "\n")
                 pending.remove(item)
         if pending:
             time.sleep(0.2)
@@ -127,7 +181,7 @@ def _compile(bdir: Path, lib: Path) -> None:
                 _log(f"still compiling {', '.join(s.name for s, _, _ in pending)} ({time.time() - t0:.0f}s)")
                 last = time.time()
     tmp = lib.with_suffix(f".tmp{os.getpid()}.so")
-    cmd = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(tmp), *[str(o) for _, o, _ in procs]]
+    cmd = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(tmp), *[str(o) for o in objects]]
     r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, env=env)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout.decode(errors='replace')}")

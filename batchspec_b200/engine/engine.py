@@ -82,7 +82,7 @@ class Engine:
         """Either ``model_dir`` (config.json + safetensors), or a configuration
         (``config`` object or ``config_name`` of the by-name table) with
         ``random_seed`` for random weights."""
-        ops.load_library()
+        ops.load_library(features=())      # the core; a part that needs more asks for it when it is built
         torch.cuda.set_device(self.device)
         runtime = Runtime(self.dtype, self.device)
         if model_dir is not None:

@@ -126,28 +126,49 @@ _SIGNATURES = {
 }
 
 
-def load_library():
-    """Load (building on first use) the kernel library.  Raises if it cannot."""
-    global _lib
-    if _lib is not None:
+_features = None       # features of the loaded library: a frozenset, or None for the library of all files
+
+
+def load_library(features=None):
+    """Load (building on first use) the kernel library.  Raises if it cannot.
+
+    ``features`` None: the loaded library if there is one, else the library of all files.  A tuple of names of
+    ``csrc.build.FEATURES``: a library that has at least the core and those (what is loaded already, if it does;
+    else one is built and loaded, and the wrappers call into it from then on)."""
+    global _lib, _features
+    if _lib is not None and (features is None or _features is None or set(features) <= _features):
         return _lib
     with _lock:
-        if _lib is not None:
+        if _lib is not None and (features is None or _features is None or set(features) <= _features):
             return _lib
-        from ..csrc.build import library_path
-        path = library_path(build=True)
+        from ..csrc.build import FEATURES, LIB_NAME, library_path
+        want = None if features is None else frozenset(features) | (_features or frozenset())
+        if want is not None and want == frozenset(FEATURES):
+            want = None
+        path = library_path(build=True, features=None if want is None else tuple(sorted(want)))
+        if path.name == LIB_NAME:
+            want = None                               # the library of all files served the request
         lib = ctypes.CDLL(str(path))
         for name, argtypes in _SIGNATURES.items():
-            fn = getattr(lib, name)
+            fn = getattr(lib, name, None)
+            if fn is None:
+                if want is None:
+                    raise KernelError(f"{path} has no entry point {name}")
+                continue                              # an entry point of a feature this library was built without
             fn.argtypes = argtypes
             fn.restype = c_longlong if name == "bspec_gemm_tc_plan" else c_int
-        _lib = lib
+        _lib, _features = lib, want
         from . import debug
         debug.apply_environment(sys.modules[__name__], lib)
         global _BOUNDS_ACTIVE
         from ..csrc.build import bounds_requested
         _BOUNDS_ACTIVE = bounds_requested()
     return _lib
+
+
+def require(*features) -> None:
+    """Make sure the loaded library has these features (a part calls this when it is built)."""
+    load_library(features=tuple(features))
 
 
 _BOUNDS_ACTIVE = False
@@ -179,7 +200,9 @@ def set_trace(buf: Optional[torch.Tensor], count: Optional[torch.Tensor]) -> Non
     ``None`` switches it off.  Set it before capturing a graph that should record."""
     lib = load_library()
     for name in _TRACE_SETTERS:
-        fn = getattr(lib, name)
+        fn = getattr(lib, name, None)
+        if fn is None:
+            continue                                  # a file of a feature the loaded library was built without
         fn.argtypes = [c_void_p, c_void_p]
         fn.restype = c_int
         _check(fn(_ptr(buf), _ptr(count)), name)
@@ -188,7 +211,7 @@ def set_trace(buf: Optional[torch.Tensor], count: Optional[torch.Tensor]) -> Non
 def library_file() -> str:
     load_library()
     from ..csrc.build import library_path
-    return str(library_path(build=False))
+    return str(library_path(build=False, features=None if _features is None else tuple(sorted(_features))))
 
 
 def launch_count() -> int:
@@ -768,7 +791,9 @@ def bounds_reports() -> list:
     lib = load_library()
     found = []
     for name in _BOUNDS_REPORTS:
-        fn = getattr(lib, name)
+        fn = getattr(lib, name, None)
+        if fn is None:
+            continue
         fn.argtypes = [ctypes.POINTER(c_int * 4)]
         fn.restype = c_int
         rec = (c_int * 4)()

@@ -61,6 +61,8 @@ class LatentAttention(Mixer):
         return specs
 
     def bind(self, params):
+        if torch.device(self.runtime.device).type == "cuda":
+            ops.require("latent")                 # the kernels of csrc/latent*.cu
         H = self.n_heads
         rows = [params["dq"], params["dkv"]] + ([params["g"]] if self.gated else [])
         self.w_down = torch.cat(rows, dim=0).contiguous()                  # [q_rank + kv_rank + rot_dim (+ H), dim]

@@ -43,6 +43,8 @@ class RoutedGelu(FeedForward):
         return specs
 
     def bind(self, params):
+        if torch.device(self.runtime.device).type == "cuda":
+            ops.require("moe")                    # the kernels of csrc/moe.cu
         self.w_router = params["router"].contiguous()
         self.b_correction = params["correction"].contiguous() if self.correction else None
         self.w_up = torch.stack([params[f"up{e}"] for e in range(self.n_experts)]).contiguous()

@@ -163,3 +163,16 @@ def test_plain_delta_rule_and_convolution():
     y = P.short_conv(x, w)
     assert y[0, 0] == pytest.approx(100 * float(x[0, 0])) and torch.allclose(y[:, 1], x[:, 1])
     assert y[4, 0] == pytest.approx(float(x[2, 0] + 10 * x[3, 0] + 100 * x[4, 0]))
+
+
+def test_kernel_library_features_leave_out_only_what_they_name():
+    from batchspec_b200.csrc import build
+    every = {p.name for p in build.sources()}
+    core = {p.name for p in build.sources(())}
+    assert {"delta.cu", "attention_generic.cu", "attention_bf16.cu", "elementwise.cu", "gemm_tcgen05.cu"} <= core
+    assert every - core == {n for names in build.FEATURES.values() for n in names}
+    assert {p.name for p in build.sources(("moe",))} == core | set(build.FEATURES["moe"])
+    assert build.lib_name(None) == build.lib_name(tuple(build.FEATURES)) == build.LIB_NAME
+    assert build.lib_name(()) != build.lib_name(("moe",)) != build.LIB_NAME
+    with pytest.raises(KeyError):
+        build.sources(("nothing",))
