@@ -53,7 +53,10 @@ CFG_C = _config(640, 256, 1e-5, 1.3, [_attention(8, 2, 64, 64, 0.1, 128, 64, 100
 # attention alone, so that nothing carries a token's content past a chunk's edge
 CFG_EDGE = _config(150, 32, 1e-5, 0.9, [_attention(2, 1, 16, 8, 0.5, 12, 16, 1000.0, None, ff=24),
                                         _attention(2, 2, 8, 16, 0.4, 12, 4, 50.0, YARN_A)])
-CONFIGS = {"A": (CFG_A, 11, 4), "B": (CFG_B, 12, 8), "C": (CFG_C, 13, 16), "EDGE": (CFG_EDGE, 14, 8)}   # config, seed, page
+# recurrent layers alone: no pages at all, only state slots
+CFG_STATE = _config(90, 40, 1e-5, 0.8, [_delta(2, 1, 16, 16, 2, ff=24), _delta(4, 4, 8, 24, 4)], loop=(0, 1, 2))
+CONFIGS = {"A": (CFG_A, 11, 4), "B": (CFG_B, 12, 8), "C": (CFG_C, 13, 16), "EDGE": (CFG_EDGE, 14, 8),
+           "STATE": (CFG_STATE, 15, 8)}                                                         # config, seed, page
 LENGTHS = {"A": [1, 6, 23, 70], "B": [2, 9, 41, 130], "C": [3, 64, 150, 333]}
 
 
@@ -458,6 +461,19 @@ def test_mixed_requests_reuse_pages_and_slots(tmp_path, name, dtype):
     for rid in ("r2", "r3"):                                # every request alone gives the same rows as in the batch
         one = H.run_steps_in_process(alone, H.whole(rid, reqs[rid]))
         _rows_agree(one, {k: got[k] for k in one}, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_model_of_recurrent_layers_alone_needs_no_pages(tmp_path, dtype):
+    cfg, seed, page = CONFIGS["STATE"]
+    folder = _folder(tmp_path, "STATE", dtype)
+    reqs = {f"q{i}": H.random_tokens(n, cfg["vocab"], 7 + i) for i, n in enumerate([1, 5, 30, 77, 12, 3])}
+    eng = _engine(folder, dtype, page, 1, max_requests=3)
+    assert not eng.cache.groups and sum(s is not None for s in eng.cache.state_tensors) == 3
+    got = H.run_steps_in_process(eng, H.mixed(reqs, seed=5, max_live=3))          # six requests through three slots
+    H.compare_with_oracle(got, folder, reqs, dtype, oracle=_oracle)
+    one = H.run_steps_in_process(eng, H.portions("q3", reqs["q3"], [2, 1, 9]))
+    _rows_agree(one, {k: got[k] for k in one}, dtype)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
