@@ -4,7 +4,7 @@
 //     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
 //
 // Three kernels, one after the other on the stream:
-//   delta_prepare     per token: causal short convolution + silu of the q, k, v channels (the inputs before the
+//   delta_prepare     per (token, head): causal short convolution + silu of the q, k, v channels (the inputs before the
 //                     portion come from the request's state), unit length of every q and k head (q also times a
 //                     scale), beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias))
 //   delta_recurrence  per (request, head, 32 or 8 value columns): the token loop over the portion with the state in
@@ -27,7 +27,11 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 30.f ? x : log
 // proj [n, ld] float32, columns [q: Gk*dim | k: Gk*dim | v: H*vdim | ... | b: H at b_off | a: H at a_off].
 // conv [C, taps] (C = 2*Gk*dim + H*vdim).  State row of a request: [H*vdim*dim matrix | (taps-1) x C inputs, oldest
 // first]; a column of the matrix holds dim numbers padded to a multiple of 4.  mix [n, C] and gates [n, 2H] (beta, then g) are float32.
-__global__ void __launch_bounds__(256)
+constexpr int DP_WARPS = 4;
+constexpr int MAX_DIM = 256;       // largest key size (a head's q or k)
+
+// One warp per head: q heads, then k heads (dim channels each, made unit length), then v heads (vdim channels).
+__global__ void __launch_bounds__(DP_WARPS * 32)
 delta_prepare_kernel(const float* __restrict__ proj, int ld, int b_off, int a_off, const void* __restrict__ conv,
                      const void* __restrict__ a_log, const void* __restrict__ dt_bias, int w_dtype,
                      const float* __restrict__ state, long long state_stride, long long tail_off,
@@ -35,42 +39,55 @@ delta_prepare_kernel(const float* __restrict__ proj, int ld, int b_off, int a_of
                      const int* __restrict__ state_slots, float* __restrict__ mix, float* __restrict__ gates, int H,
                      int Gk, int dim, int vdim, int taps, float q_scale, float unit_eps) {
   bspec::pdl_prologue(60);
-  extern __shared__ float ys[];                    // [C]
   const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (blockIdx.y == 0) {
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+      const float b = proj[(size_t)t * ld + b_off + h], a = proj[(size_t)t * ld + a_off + h];
+      gates[(size_t)t * 2 * H + h] = 1.f / (1.f + expf(-b));
+      const float rate = expf(load_as_f32(a_log, w_dtype, h)) * softplus_f(a + load_as_f32(dt_bias, w_dtype, h));
+      gates[(size_t)t * 2 * H + H + h] = expf(-rate);
+    }
+  }
+  const int slot = blockIdx.y * DP_WARPS + warp;
+  if (slot >= 2 * Gk + H) return;
   const int e = tok_entry[t];
   const int i = t - qo_indptr[e];                  // index of the token in its portion
   const int C = 2 * Gk * dim + H * vdim;
   const float* tail = state + (size_t)state_slots[e] * state_stride + tail_off;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  const bool is_v = slot >= 2 * Gk;
+  const int width = is_v ? vdim : dim;
+  const int c0 = is_v ? 2 * Gk * dim + (slot - 2 * Gk) * vdim : slot * dim;
+  float* row = mix + (size_t)t * C;
+  auto convolved = [&](int c) {                    // silu of the causal convolution of channel c, oldest input first
     float y = 0.f;
-    for (int j = taps - 1; j >= 0; --j) {          // oldest input first
+    for (int j = taps - 1; j >= 0; --j) {
       const int rel = i - j;
       const float x = rel >= 0 ? proj[(size_t)(t - j) * ld + c] : tail[(size_t)(rel + taps - 1) * C + c];
       y += load_as_f32(conv, w_dtype, (size_t)c * taps + (taps - 1 - j)) * x;
     }
-    ys[c] = silu_f(y);
+    return silu_f(y);
+  };
+  if (is_v) {
+    for (int d = lane; d < width; d += 32) row[c0 + d] = convolved(c0 + d);
+    return;
   }
-  __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  float* row = mix + (size_t)t * C;
-  for (int head = warp; head < 2 * Gk; head += nwarps) {        // q heads, then k heads
-    const float* y = ys + head * dim;
-    float ss = 0.f;
-    for (int d = lane; d < dim; d += 32) ss += y[d] * y[d];
-    ss = warp_sum(ss);
-    const float r = (head < Gk ? q_scale : 1.f) / sqrtf(ss + unit_eps);
-    for (int d = lane; d < dim; d += 32) row[head * dim + d] = y[d] * r;
+  float y[8];                                      // dim <= 256
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int d = lane + 32 * k;
+    y[k] = d < width ? convolved(c0 + d) : 0.f;
+    ss += y[k] * y[k];
   }
-  for (int c = 2 * Gk * dim + threadIdx.x; c < C; c += blockDim.x) row[c] = ys[c];
-  for (int h = threadIdx.x; h < H; h += blockDim.x) {
-    const float b = proj[(size_t)t * ld + b_off + h], a = proj[(size_t)t * ld + a_off + h];
-    gates[(size_t)t * 2 * H + h] = 1.f / (1.f + expf(-b));
-    const float rate = expf(load_as_f32(a_log, w_dtype, h)) * softplus_f(a + load_as_f32(dt_bias, w_dtype, h));
-    gates[(size_t)t * 2 * H + H + h] = expf(-rate);
+  ss = warp_sum(ss);
+  const float r = (slot < Gk ? q_scale : 1.f) / sqrtf(ss + unit_eps);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int d = lane + 32 * k;
+    if (d < width) row[c0 + d] = y[k] * r;
   }
 }
-
-constexpr int MAX_DIM = 256;
 
 // LANES: lanes that share one column of S; R: floats of the column that one lane holds (a multiple of 4, dim <=
 // LANES R); COLS: value columns of a block.  Lane r holds rows 4 LANES c + 4 r + {0..3} for c < R / 4, so that the
@@ -252,17 +269,12 @@ BSPEC_API int bspec_delta_prepare(const float* proj, int n, int ld, int b_off, i
                                   int dim, int vdim, int taps, float q_scale, float unit_eps, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (H <= 0 || Gk <= 0 || H % Gk != 0 || taps < 1) return (int)cudaErrorInvalidValue;
-  const size_t smem = (size_t)(2 * Gk * dim + H * vdim) * sizeof(float);
-  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-  static bool raised[bspec::kMaxDevices] = {};
-  if (smem > 48 * 1024 && !raised[bspec::current_device()]) {
-    cudaError_t e = cudaFuncSetAttribute(delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e != cudaSuccess) return (int)e;
-    raised[bspec::current_device()] = true;
-  }
-  BSPEC_LAUNCH(delta_prepare_kernel, n, 256, smem, stream, proj, ld, b_off, a_off, conv, a_log, dt_bias, w_dtype, state,
-               state_stride, tail_off, qo_indptr, tok_entry, state_slots, mix, gates, H, Gk, dim, vdim, taps, q_scale,
-               unit_eps);
+  if (dim > 256) return (int)cudaErrorInvalidValue;
+  const dim3 grid(n, (2 * Gk + H + DP_WARPS - 1) / DP_WARPS);
+  if (grid.y > 65535) return (int)cudaErrorInvalidConfiguration;
+  BSPEC_LAUNCH(delta_prepare_kernel, grid, DP_WARPS * 32, 0, stream, proj, ld, b_off, a_off, conv, a_log, dt_bias, w_dtype,
+               state, state_stride, tail_off, qo_indptr, tok_entry, state_slots, mix, gates, H, Gk, dim, vdim, taps,
+               q_scale, unit_eps);
   return BSPEC_LAUNCH_CHECK();
 }
 
