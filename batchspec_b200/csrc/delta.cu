@@ -9,7 +9,7 @@
 //                     scale), beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias))
 //   delta_recurrence  per (request, head, 32 or 8 value columns): the token loop over the portion with the state in
 //                     registers (a column of S is spread over four lanes), state read at the start and written at
-//                     the end; one block per request also moves the convolutions' inputs on
+//                     the end; the request's blocks also move the convolutions' inputs on
 //   gated_rmsnorm     per (token, head): o / rms(o) * w * silu(gate)
 //
 // The order of every sum depends on the sizes alone, not on how a request was cut into portions or on what else is
@@ -117,11 +117,13 @@ delta_recurrence_kernel(const float* __restrict__ mix, const float* __restrict__
   const int C = 2 * Gk * dim + H * vdim;
   float* srow = state + (size_t)state_slots[e] * state_stride;
   if (n <= 0) return;
-  if (blockIdx.x == 0 && h == 0 && taps > 1) {
+  if (taps > 1) {
     // the convolutions' inputs: slot s holds the input at index n + s - (taps - 1) of this portion, or what an
-    // older slot held; ascending s, so that a slot is read before it is overwritten
+    // older slot held; ascending s, so that a slot is read before it is overwritten.  The request's blocks share
+    // the channels (a thread moves all slots of its channel), so that no block is the step's long pole.
     float* tail = srow + tail_off;
-    for (int c = threadIdx.x; c < C; c += NT)
+    const int share = blockIdx.y * gridDim.x + blockIdx.x, shares = gridDim.y * gridDim.x;
+    for (int c = share * NT + threadIdx.x; c < C; c += shares * NT)
       for (int s = 0; s < taps - 1; ++s) {
         const int rel = n + s - (taps - 1);
         tail[(size_t)s * C + c] = rel >= 0 ? proj[(size_t)(q_begin + rel) * ld + c] : tail[(size_t)(s + n) * C + c];
