@@ -406,6 +406,47 @@ def test_delta_rule_kernels_over_portions_and_reused_slots(ops, Hh, G, dk, dv, t
     assert (torch.cat([y1, y2]).double().cpu() - want).abs().max() <= 2e-4 * max(1.0, want.abs().max().item())
 
 
+@pytest.mark.parametrize("Hh,G,dk,dv,n_req", [(16, 8, 64, 128, 10), (32, 4, 128, 64, 6), (12, 12, 36, 96, 9)])
+def test_delta_rule_recurrence_with_many_requests(ops, Hh, G, dk, dv, n_req):
+    """Enough (request, head) pairs that the kernel takes its form of 32 columns per block (with few it spreads a
+    column over 16 lanes): requests of 1 to 40 tokens in two steps against the plain recurrence."""
+    taps = 3
+    C = 2 * G * dk + Hh * dv
+    ld = C + Hh * dv + 2 * Hh
+    tail_off = Hh * dv * (-(-dk // 4) * 4)
+    gen = torch.Generator(device=DEV).manual_seed(Hh + dk)
+    state = torch.zeros(n_req, -(-(tail_off + (taps - 1) * C) // 4) * 4, device=DEV)
+    lens = [[1 + (7 * i) % 23 for i in range(n_req)], [1 + (5 * i + 3) % 17 for i in range(n_req)]]
+    conv = torch.randn(C, taps, device=DEV, generator=gen) * 0.7
+    a_log, dt_bias = torch.randn(Hh, device=DEV, generator=gen) - 2, torch.randn(Hh, device=DEV, generator=gen)
+    proj = [torch.randn(lens[0][i] + lens[1][i], ld, device=DEV, generator=gen) for i in range(n_req)]
+    got = [[] for _ in range(n_req)]
+    at = [0] * n_req
+    for step in lens:
+        rows = torch.cat([proj[i][at[i]:at[i] + step[i]] for i in range(n_req)]).contiguous()
+        ctx = SimpleNamespace(qo_indptr=_i32([0] + list(np.cumsum(step))), n_entries=n_req,
+                              tok_entry=torch.cat([torch.full((k,), i) for i, k in enumerate(step)]).to(DEV, torch.int32),
+                              state_slots=_i32(range(n_req)))
+        mix, gates = ops.delta_prepare(rows, ld - 2 * Hh, ld - Hh, conv, a_log, dt_bias, state, tail_off, ctx, Hh, G, dk,
+                                       dv, taps, dk ** -0.5, 1e-6)
+        o = ops.delta_recurrence(mix, gates, rows, state, tail_off, ctx, Hh, G, dk, dv, taps)
+        off = 0
+        for i in range(n_req):
+            got[i].append(o[off:off + step[i]])
+            off += step[i]
+            at[i] += step[i]
+    for i in range(n_req):
+        x = proj[i].double().cpu()
+        T = x.shape[0]
+        y = P.silu(P.short_conv(x[:, :C], conv.double().cpu()))
+        q = (P.unit(y[:, :G * dk].view(T, G, dk)) * dk ** -0.5).repeat_interleave(Hh // G, dim=1)
+        k = P.unit(y[:, G * dk:2 * G * dk].view(T, G, dk)).repeat_interleave(Hh // G, dim=1)
+        beta = torch.sigmoid(x[:, ld - 2 * Hh:ld - Hh])
+        g = torch.exp(-torch.exp(a_log.double().cpu()) * P.softplus(x[:, ld - Hh:] + dt_bias.double().cpu()))
+        want = P.gated_delta_rule(q, k, y[:, 2 * G * dk:].view(T, Hh, dv), beta, g).reshape(T, -1)
+        assert (torch.cat(got[i]).double().cpu() - want).abs().max() <= 2e-4 * max(1.0, want.abs().max().item()), i
+
+
 # ------------------------------------------------------------------------------------------- the engine
 
 @pytest.mark.parametrize("dtype", DTYPES)
