@@ -96,7 +96,7 @@ delta_prepare_kernel(const float* __restrict__ proj, int ld, int b_off, int a_of
 // lanes and a block holds 8 columns, which makes four times as many warps with dependent chains a quarter as long.  Per token both read-outs are taken from the state before the write,
 //     a = S^T k,  b = S^T q,  u = beta (v - g a),  o = g b + u (k . q),  S <- g S + k u^T,
 // which is the rule above with o = (g S + k u^T)^T q multiplied out: one pass over the registers for the three sums
-// (reduced over the column's lanes together), one for the update.  The next tile of tokens is copied into the
+// (reduced over the column's lanes together), one for the update.  The 16-lane form takes two tokens per pass.  The next tile of tokens is copied into the
 // other half of the staging buffers while the current one is worked on.
 template <int R, int COLS, int LANES>
 __global__ void __launch_bounds__(COLS * LANES)
@@ -112,6 +112,7 @@ delta_recurrence_kernel(const float* __restrict__ mix, const float* __restrict__
   __shared__ __align__(16) float ks[2][TILE][DP];
   __shared__ float vs[2][TILE][COLS];
   __shared__ float bg[2][TILE][2];
+  __shared__ float sc[TILE / 2][4];                // products between the two tokens of every pair of the tile
   const int e = blockIdx.z, h = blockIdx.y;
   const int q_begin = qo_indptr[e], n = qo_indptr[e + 1] - q_begin;
   const int C = 2 * Gk * dim + H * vdim;
@@ -185,27 +186,9 @@ delta_recurrence_kernel(const float* __restrict__ mix, const float* __restrict__
     __pipeline_wait_prior(0);
     __syncthreads();                                // the tile is there, and every thread is done with the other half
     if (t0 + TILE < n) stage(t0 + TILE, buf ^ 1);
-    // the token's k and q live in registers for both passes; with few floats per lane the next token's are
-    // fetched before this token's sums are reduced
-    constexpr bool AHEAD = R <= 16;
-    float4 kr[R / 4], qr[R / 4], kn[AHEAD ? R / 4 : 1], qn[AHEAD ? R / 4 : 1];
-    auto fetch = [&](int tt, float4* kd, float4* qd) {
-#pragma unroll
-      for (int c = 0; c < R / 4; ++c) {
-        const int row = 4 * LANES * c + 4 * r;      // rows beyond dim hold zeros in the state and in the staging
-        kd[c] = *reinterpret_cast<const float4*>(&ks[buf][tt][row]);
-        qd[c] = *reinterpret_cast<const float4*>(&qs[buf][tt][row]);
-      }
-    };
-    if (AHEAD) fetch(0, kn, qn);
-    for (int tt = 0; tt < nt; ++tt) {
+    // one token: both read-outs from the state before the write, then the write
+    auto one_token = [&](int tt, const float4* kr, const float4* qr) {
       const float beta = bg[buf][tt][0], g = bg[buf][tt][1], vj = vs[buf][tt][col];
-      if (AHEAD) {
-#pragma unroll
-        for (int c = 0; c < R / 4; ++c) { kr[c] = kn[c]; qr[c] = qn[c]; }
-      } else {
-        fetch(tt, kr, qr);
-      }
       float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f, kq = 0.f;
 #pragma unroll
       for (int c = 0; c < R / 4; ++c) {
@@ -214,7 +197,6 @@ delta_recurrence_kernel(const float* __restrict__ mix, const float* __restrict__
         b0 += s[4 * c] * q4.x; b1 += s[4 * c + 1] * q4.y; b0 += s[4 * c + 2] * q4.z; b1 += s[4 * c + 3] * q4.w;
         kq += k4.x * q4.x; kq += k4.y * q4.y; kq += k4.z * q4.z; kq += k4.w * q4.w;
       }
-      if (AHEAD && tt + 1 < nt) fetch(tt + 1, kn, qn);
       float a = a0 + a1, b = b0 + b1;
 #pragma unroll
       for (int o = 1; o < LANES; o <<= 1) {
@@ -231,6 +213,93 @@ delta_recurrence_kernel(const float* __restrict__ mix, const float* __restrict__
         s[4 * c + 1] = fmaf(k4.y, u, g * s[4 * c + 1]);
         s[4 * c + 2] = fmaf(k4.z, u, g * s[4 * c + 2]);
         s[4 * c + 3] = fmaf(k4.w, u, g * s[4 * c + 3]);
+      }
+    };
+    auto fetch = [&](int tt, float4* kd, float4* qd) {
+#pragma unroll
+      for (int c = 0; c < R / 4; ++c) {
+        const int row = 4 * LANES * c + 4 * r;      // rows beyond dim hold zeros in the state and in the staging
+        kd[c] = *reinterpret_cast<const float4*>(&ks[buf][tt][row]);
+        qd[c] = *reinterpret_cast<const float4*>(&qs[buf][tt][row]);
+      }
+    };
+    if constexpr (LANES == 16) {
+      // The long chain of one prompt: two tokens per pass.  With a = S^T k and b = S^T q of BOTH tokens taken from
+      // the state before either write, and the tokens' mutual products (the same for every column, formed once
+      // per tile below),
+      //   u1 = beta1 (v1 - g1 a1)                    o1 = g1 b1 + u1 (k1.q1)
+      //   u2 = beta2 (v2 - g2 (g1 a2 + u1 (k1.k2)))  o2 = g2 (g1 b2 + u1 (k1.q2)) + u2 (k2.q2)
+      //   S <- g1 g2 S + g2 u1 k1 + u2 k2,
+      // which is the rule applied twice, multiplied out: one round of reductions and one pass over the registers
+      // for two tokens.
+      {
+        const int pr = min((int)(threadIdx.x >> 4), TILE / 2 - 1), sub = threadIdx.x & 15;
+        const float *k1 = ks[buf][2 * pr], *q1 = qs[buf][2 * pr], *k2 = ks[buf][2 * pr + 1], *q2 = qs[buf][2 * pr + 1];
+        float x0 = 0.f, x1 = 0.f, x2 = 0.f, x3 = 0.f;
+        for (int d = sub; d < dimp; d += 16) {
+          x0 += k1[d] * q1[d]; x1 += k1[d] * k2[d]; x2 += k1[d] * q2[d]; x3 += k2[d] * q2[d];
+        }
+#pragma unroll
+        for (int o = 1; o < 16; o <<= 1) {
+          x0 += __shfl_xor_sync(0xffffffffu, x0, o); x1 += __shfl_xor_sync(0xffffffffu, x1, o);
+          x2 += __shfl_xor_sync(0xffffffffu, x2, o); x3 += __shfl_xor_sync(0xffffffffu, x3, o);
+        }
+        if (sub == 0 && (int)(threadIdx.x >> 4) < TILE / 2 && 2 * pr + 1 < nt) {
+          sc[pr][0] = x0; sc[pr][1] = x1; sc[pr][2] = x2; sc[pr][3] = x3;
+        }
+      }
+      __syncthreads();
+      const int np = nt >> 1;
+      float4 k1n[R / 4], q1n[R / 4], k2n[R / 4], q2n[R / 4];
+      if (np > 0) { fetch(0, k1n, q1n); fetch(1, k2n, q2n); }
+      for (int pp = 0; pp < np; ++pp) {
+        float4 k1[R / 4], q1[R / 4], k2[R / 4], q2[R / 4];
+#pragma unroll
+        for (int c = 0; c < R / 4; ++c) { k1[c] = k1n[c]; q1[c] = q1n[c]; k2[c] = k2n[c]; q2[c] = q2n[c]; }
+        const int t1 = 2 * pp, t2 = 2 * pp + 1;
+        const float beta1 = bg[buf][t1][0], g1 = bg[buf][t1][1], v1 = vs[buf][t1][col];
+        const float beta2 = bg[buf][t2][0], g2 = bg[buf][t2][1], v2 = vs[buf][t2][col];
+        const float kq11 = sc[pp][0], kk12 = sc[pp][1], kq12 = sc[pp][2], kq22 = sc[pp][3];
+        float a1 = 0.f, b1 = 0.f, a2 = 0.f, b2 = 0.f;
+#pragma unroll
+        for (int c = 0; c < R / 4; ++c) {
+          a1 += s[4 * c] * k1[c].x; a1 += s[4 * c + 1] * k1[c].y; a1 += s[4 * c + 2] * k1[c].z; a1 += s[4 * c + 3] * k1[c].w;
+          b1 += s[4 * c] * q1[c].x; b1 += s[4 * c + 1] * q1[c].y; b1 += s[4 * c + 2] * q1[c].z; b1 += s[4 * c + 3] * q1[c].w;
+          a2 += s[4 * c] * k2[c].x; a2 += s[4 * c + 1] * k2[c].y; a2 += s[4 * c + 2] * k2[c].z; a2 += s[4 * c + 3] * k2[c].w;
+          b2 += s[4 * c] * q2[c].x; b2 += s[4 * c + 1] * q2[c].y; b2 += s[4 * c + 2] * q2[c].z; b2 += s[4 * c + 3] * q2[c].w;
+        }
+        if (pp + 1 < np) { fetch(2 * pp + 2, k1n, q1n); fetch(2 * pp + 3, k2n, q2n); }
+#pragma unroll
+        for (int o = 1; o < LANES; o <<= 1) {
+          a1 += __shfl_xor_sync(0xffffffffu, a1, o); b1 += __shfl_xor_sync(0xffffffffu, b1, o);
+          a2 += __shfl_xor_sync(0xffffffffu, a2, o); b2 += __shfl_xor_sync(0xffffffffu, b2, o);
+        }
+        const float u1 = beta1 * (v1 - g1 * a1);
+        const float u2 = beta2 * (v2 - g2 * (g1 * a2 + u1 * kk12));
+        if (live && r == 0) {
+          float* op = out + (size_t)(q_begin + t0 + t1) * H * vdim + h * vdim + j;
+          op[0] = g1 * b1 + u1 * kq11;
+          op[(size_t)H * vdim] = g2 * (g1 * b2 + u1 * kq12) + u2 * kq22;
+        }
+        const float c0 = g1 * g2, c1 = g2 * u1;
+#pragma unroll
+        for (int c = 0; c < R / 4; ++c) {
+          s[4 * c] = fmaf(k2[c].x, u2, fmaf(k1[c].x, c1, c0 * s[4 * c]));
+          s[4 * c + 1] = fmaf(k2[c].y, u2, fmaf(k1[c].y, c1, c0 * s[4 * c + 1]));
+          s[4 * c + 2] = fmaf(k2[c].z, u2, fmaf(k1[c].z, c1, c0 * s[4 * c + 2]));
+          s[4 * c + 3] = fmaf(k2[c].w, u2, fmaf(k1[c].w, c1, c0 * s[4 * c + 3]));
+        }
+      }
+      if (nt & 1) {                                 // the portion's last token
+        float4 kr[R / 4], qr[R / 4];
+        fetch(nt - 1, kr, qr);
+        one_token(nt - 1, kr, qr);
+      }
+    } else {
+      for (int tt = 0; tt < nt; ++tt) {
+        float4 kr[R / 4], qr[R / 4];
+        fetch(tt, kr, qr);
+        one_token(tt, kr, qr);
       }
     }
   }
